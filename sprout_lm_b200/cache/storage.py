@@ -3,7 +3,8 @@
 ``plan_groups`` sorts the model's cache slots into groups by what their mixers keep (all
 positions, or a window of them); the host-side ``CacheManager`` hands out page ids per
 group, and every slot of a group has buffers of its own indexed by those ids:
-keys and values [pages, kv_heads, page_tokens, head_dim] in the compute dtype.
+keys [pages, kv_heads, page_tokens, head_dim] and values [pages, kv_heads, page_tokens, value width]
+in the compute dtype (no value buffer for a mixer that keeps one row per token and reads both from it).
 """
 from __future__ import annotations
 
@@ -41,7 +42,7 @@ def state_slot_count(model, max_requests: int) -> int:
 
 def cache_bytes_per_token(model, dtype: torch.dtype) -> int:
     item = torch.empty((), dtype=dtype).element_size()
-    return sum(2 * spec.kv_heads * spec.head_dim * item for spec in model.cache_specs() if spec is not None)
+    return sum(spec.kv_heads * (spec.head_dim + spec.value_width) * item for spec in model.cache_specs() if spec is not None)
 
 
 class CapacityError(RuntimeError):
@@ -58,7 +59,7 @@ def check_capacity(model, slot_group: list[int], num_pages, page_tokens: int) ->
     runtime = model.runtime
     item = torch.empty((), dtype=runtime.dtype).element_size()
     counts = num_pages if not isinstance(num_pages, int) else [num_pages] * (max(slot_group, default=0) + 1)
-    need = sum(2 * counts[slot_group[slot]] * spec.kv_heads * page_tokens * spec.head_dim * item
+    need = sum(counts[slot_group[slot]] * spec.kv_heads * page_tokens * (spec.head_dim + spec.value_width) * item
                for slot, spec in enumerate(model.cache_specs()) if spec is not None)
     free, _ = torch.cuda.mem_get_info(runtime.device)
     if need + RESERVE_BYTES > free:
@@ -83,7 +84,9 @@ class CacheStorage:
             pages = manager.pools[slot_group[slot]].num_pages
             shape = (pages, spec.kv_heads, self.page_tokens, spec.head_dim)
             self.keys.append(torch.zeros(shape, dtype=runtime.dtype, device=runtime.device))
-            self.values.append(torch.zeros(shape, dtype=runtime.dtype, device=runtime.device))
+            # a mixer that reads its values out of the key rows has no value buffer (the view's v is None)
+            self.values.append(torch.zeros((*shape[:3], spec.value_width), dtype=runtime.dtype, device=runtime.device)
+                               if spec.value_width else None)
         self.states = []
         for spec in model.state_specs():
             if spec is None:

@@ -3,7 +3,7 @@
 A configuration class has ``from_dict(raw) -> config`` (raising ConfigError),
 ``to_dict()``, ``model_spec() -> ModelSpec`` and ``with_eos(ids)``.  The
 architecture of a model folder is ``architectures[0]`` of its config.json when
-that is present, otherwise its ``model_type`` (the reference's fixture has
+that is present (or its ``architecture``, a single name), otherwise its ``model_type`` (the reference's fixture has
 ``"architectures": null`` and is recognised by ``model_type`` alone,
 src/qwen.ts:17).
 """
@@ -35,6 +35,8 @@ def architecture_name(raw: Mapping[str, Any]) -> str:
     if not isinstance(raw, Mapping):
         raise ConfigError("config.json must hold a JSON object.")
     names = raw.get("architectures")
+    if isinstance(raw.get("architecture"), str) and not names:
+        names = [raw["architecture"]]            # a config.json that names its one architecture in a string
     if isinstance(names, list) and names:
         name = names[0]
         if name not in _BY_ARCHITECTURE:

@@ -29,13 +29,15 @@ class PartSpec:
 class LayerSpec:
     """One layer: the arrangement (``block``) and the parts it arranges.
 
-    ``prefix`` is the layer's prefix in checkpoint tensor names.
+    ``prefix`` is the layer's prefix in checkpoint tensor names; ``options`` are constants of the
+    arrangement itself (a post_norm block's ``alpha``).
     """
     block: str
     prefix: str
     mixer: PartSpec
     feed_forward: PartSpec
     norms: tuple[PartSpec, ...]
+    options: Mapping[str, Any] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)
@@ -66,6 +68,7 @@ class ModelSpec:
     head: PartSpec
     eos_token_ids: tuple[int, ...]
     ignorable_tensors: tuple[str, ...] = ()
+    stream: PartSpec | None = None       # what goes from one layer call to the next (None: the call's result)
 
     def __post_init__(self):
         for call in self.order:

@@ -1,0 +1,468 @@
+// Kernels of layers that cache a low-rank latent instead of per-head keys and values, and of the
+// arrangements such models use around their sublayers.  All arithmetic is float32; the element
+// type of activations and of the cache (float or bfloat16) is a template parameter.
+//
+//  * scale_cast:        y = alpha * x (float32), h = T(x): the two readers of a stream whose norm
+//                       comes after the sum (the sublayer reads h, its output is added to y).
+//  * sum_norm:          x = rmsnorm(y) * gain, and for the next sublayer y = alpha * x, h = T(x).
+//  * polynorm:          a N(z) + b N(z^2) + c N(z^3) + e with N = division by the row's root mean square.
+//  * latent_kv_append:  per token a row [latent (rank) | shared rotary key part]: the latent is
+//                       RMS-normed with a learned weight, the key part rotated by the token's
+//                       position, and both are stored as one row of a paged cache with one head.
+//  * latent_query_tail: the rotated part of every query head, copied behind the head's latent
+//                       query (the row a latent attention kernel multiplies with a cache row).
+//  * headwise_gemm:     out[t, h, :] = W[h] a[t, h, :], one small matrix per head.
+//  * latent_attention_simple: causal attention of (token, head) rows over the latent cache rows,
+//                       all heads reading the same row; the value is the row's first `rank`
+//                       elements; optional sink term in the softmax denominator.
+//  * depth_average:     keeps a layer's result in a history and replaces the stream by a weighted
+//                       sum of the history so far.
+//  * softcap:           x = cap * tanh(x / cap), in place.
+#include "common.cuh"
+
+namespace {
+
+// ---------------------------------------------------------------- scale_cast
+template <typename TO>
+__global__ void scale_cast_kernel(const float* __restrict__ x, float* __restrict__ y, TO* __restrict__ h,
+                                  float alpha, long long count) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
+    const float v = x[i];
+    y[i] = alpha * v;
+    if (h) h[i] = from_float<TO>(v);
+  }
+}
+
+// ---------------------------------------------------------------- sum_norm
+// One block per row.  `x` may be `y` itself; y2 may be y too (every element is read by the thread
+// that later writes it).
+template <typename TO>
+__global__ void __launch_bounds__(256)
+sum_norm_kernel(const float* y, const float* __restrict__ gain, float* x, float* y2, TO* __restrict__ h,
+                int hidden, float eps, float alpha) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t row = (size_t)blockIdx.x * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) { const float v = y[row + i]; ss = fmaf(v, v, ss); }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = (y[row + i] * scale) * gain[i];
+    x[row + i] = v;
+    if (y2) y2[row + i] = alpha * v;
+    if (h) h[row + i] = from_float<TO>(v);
+  }
+}
+
+// ---------------------------------------------------------------- polynorm
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+polynorm_kernel(const TI* __restrict__ z, TO* __restrict__ out, const float* __restrict__ coef, int width, float eps) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t row = (size_t)blockIdx.x * width;
+  float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = to_float(z[row + i]);
+    const float v2 = v * v, v3 = v2 * v;
+    s2 = fmaf(v, v, s2);
+    s4 = fmaf(v2, v2, s4);
+    s6 = fmaf(v3, v3, s6);
+  }
+  s2 = block_sum(s2, scratch);
+  s4 = block_sum(s4, scratch);
+  s6 = block_sum(s6, scratch);
+  const float r1 = 1.0f / sqrtf(s2 / (float)width + eps);
+  const float r2 = 1.0f / sqrtf(s4 / (float)width + eps);
+  const float r3 = 1.0f / sqrtf(s6 / (float)width + eps);
+  const float a = coef[0], b = coef[1], c = coef[2], e = coef[3];
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = to_float(z[row + i]);
+    const float v2 = v * v, v3 = v2 * v;
+    out[row + i] = from_float<TO>(a * (v * r1) + b * (v2 * r2) + c * (v3 * r3) + e);
+  }
+}
+
+// ---------------------------------------------------------------- latent_kv_append
+// src row t (float32, row stride ld): [rank latent values | rot shared key values].  The cache
+// row of token t: page = table[seq][pos / page_tokens], slot pos % page_tokens, `rank + rot` wide.
+template <typename TC>
+__global__ void __launch_bounds__(128)
+latent_kv_append_kernel(const float* __restrict__ src, int ld, const float* __restrict__ weight,
+                        const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                        const int* __restrict__ block_table, int table_stride,
+                        const float* __restrict__ cos_table, const float* __restrict__ sin_table, int table_positions,
+                        int rotary_dim, int interleaved, TC* __restrict__ cache, int rank, int rot, int page_tokens,
+                        int num_pages, float eps, int* status) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const float* row = src + (size_t)t * ld;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) { const float v = row[i]; ss = fmaf(v, v, ss); }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)rank + eps);
+  const int pos = positions[t];
+  const int page = block_table[(size_t)seq_of_token[t] * table_stride + pos / page_tokens];
+  if (page < 0 || page >= num_pages) {
+    if (threadIdx.x == 0) atomicOr(status, SPROUT_STATUS_BAD_PAGE);
+    return;
+  }
+  TC* dst = cache + ((size_t)page * page_tokens + pos % page_tokens) * (rank + rot);
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) dst[i] = from_float<TC>((row[i] * scale) * weight[i]);
+  const float* key = row + rank;
+  const int half = rotary_dim / 2;
+  int p = pos;
+  if (half > 0 && (p < 0 || p >= table_positions)) {
+    if (threadIdx.x == 0) atomicOr(status, SPROUT_STATUS_BAD_POSITION);
+    p = 0;
+  }
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+    const float c = cos_table[(size_t)p * half + i], s = sin_table[(size_t)p * half + i];
+    const float u = key[a], v = key[b];
+    dst[rank + a] = from_float<TC>(u * c - v * s);
+    dst[rank + b] = from_float<TC>(v * c + u * s);
+  }
+  for (int i = rotary_dim + threadIdx.x; i < rot; i += blockDim.x) dst[rank + i] = from_float<TC>(key[i]);
+}
+
+// ---------------------------------------------------------------- latent_query_tail
+// q [tokens, heads, dim + rot] -> qlat[t, h, rank + (0..rot)] = rotation of q[t, h, dim + (0..rot)].
+template <typename T>
+__global__ void latent_query_tail_kernel(const T* __restrict__ q, T* __restrict__ qlat, const int* __restrict__ positions,
+                                         const float* __restrict__ cos_table, const float* __restrict__ sin_table,
+                                         int table_positions, int rotary_dim, int interleaved, int heads, int dim,
+                                         int rot, int rank, int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int half = rotary_dim / 2;
+  int p = positions[t];
+  if (half > 0 && (p < 0 || p >= table_positions)) {
+    if (threadIdx.x == 0) atomicOr(status, SPROUT_STATUS_BAD_POSITION);
+    p = 0;
+  }
+  const int pairs_and_rest = half + (rot - rotary_dim);
+  for (int idx = threadIdx.x; idx < heads * pairs_and_rest; idx += blockDim.x) {
+    const int h = idx / pairs_and_rest, i = idx % pairs_and_rest;
+    const T* src = q + ((size_t)t * heads + h) * (dim + rot) + dim;
+    T* dst = qlat + ((size_t)t * heads + h) * (rank + rot) + rank;
+    if (i < half) {
+      const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+      const float c = cos_table[(size_t)p * half + i], s = sin_table[(size_t)p * half + i];
+      const float u = to_float(src[a]), v = to_float(src[b]);
+      dst[a] = from_float<T>(u * c - v * s);
+      dst[b] = from_float<T>(v * c + u * s);
+    } else {
+      const int d = rotary_dim + (i - half);
+      dst[d] = src[d];
+    }
+  }
+}
+
+// ---------------------------------------------------------------- headwise_gemm
+// out[t, h, n] = sum_k a[t, h, k] * w[h, n, k]; one thread per output element group, ascending k,
+// so a value does not depend on the number of rows in the call.
+constexpr int HB = 64, HK = 16, HTHREADS = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(HTHREADS)
+headwise_gemm_kernel(const T* __restrict__ A, long long a_row, long long a_head, const T* __restrict__ W,
+                     T* __restrict__ out, long long o_row, long long o_head, int M, int N, int K) {
+  __shared__ float As[HK][HB + 4];
+  __shared__ float Ws[HK][HB + 4];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x, ty = tid / 16, tx = tid % 16;
+  const int head = blockIdx.z;
+  const int m0 = blockIdx.y * HB, n0 = blockIdx.x * HB;
+  const T* a = A + head * a_head;
+  const T* w = W + (size_t)head * N * K;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += HK) {
+#pragma unroll
+    for (int i = 0; i < (HB * HK) / HTHREADS; i++) {
+      const int idx = tid + i * HTHREADS;
+      const int row = idx / HK, k = idx % HK;
+      const int gm = m0 + row, gn = n0 + row, gk = k0 + k;
+      As[k][row] = (gm < M && gk < K) ? to_float(a[(size_t)gm * a_row + gk]) : 0.f;
+      Ws[k][row] = (gn < N && gk < K) ? to_float(w[(size_t)gn * K + gk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < HK; k++) {
+      float av[4], wv[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) av[i] = As[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; j++) wv[j] = Ws[k][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int gm = m0 + ty * 4 + i;
+    if (gm >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int gn = n0 + tx * 4 + j;
+      if (gn < N) out[(size_t)gm * o_row + head * o_head + gn] = from_float<T>(acc[i][j]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------- latent_attention_simple
+// One block per (token, head).  Keys are walked in chunks of 128 aligned to absolute position with a
+// running maximum and sum that start from the head's sink (maximum = sink, sum = 1) when one is given.
+constexpr int CHUNK = 128;
+constexpr int MAX_V = 8;     // value elements per thread: rank <= MAX_V * CHUNK
+
+template <typename T>
+__global__ void __launch_bounds__(CHUNK)
+latent_attention_simple_kernel(const T* __restrict__ qlat, const T* __restrict__ cache,
+                               const int* __restrict__ block_table, int table_stride,
+                               const int* __restrict__ seq_of_token, const int* __restrict__ positions,
+                               const float* __restrict__ sink, T* __restrict__ out, int heads, int width, int rank,
+                               int page_tokens, int num_pages, float scale, int* status) {
+  extern __shared__ float smem[];
+  float* qs = smem;                       // width
+  float* probs = qs + width;              // CHUNK
+  float* scratch = probs + CHUNK;         // 34
+  long long* row_offset = (long long*)(scratch + 34 + ((width & 1) ? 1 : 0));
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int pos = positions[t];
+  const int* table = block_table + (size_t)seq_of_token[t] * table_stride;
+  for (int d = tid; d < width; d += CHUNK) qs[d] = to_float(qlat[((size_t)t * heads + h) * width + d]);
+  __syncthreads();
+  float m_run = sink ? sink[h] : -INFINITY, l_run = sink ? 1.f : 0.f;
+  float acc[MAX_V];
+#pragma unroll
+  for (int i = 0; i < MAX_V; i++) acc[i] = 0.f;
+  for (int base = 0; base <= pos; base += CHUNK) {
+    const int p = base + tid;
+    bool valid = p <= pos;
+    long long offset = 0;
+    if (valid) {
+      const int page = table[p / page_tokens];
+      if (page < 0 || page >= num_pages) {
+        atomicOr(status, SPROUT_STATUS_BAD_PAGE);
+        valid = false;
+      } else {
+        offset = ((long long)page * page_tokens + (p % page_tokens)) * width;
+      }
+    }
+    float s = -INFINITY;
+    if (valid) {
+      const T* key = cache + offset;
+      float dot = 0.f;
+      for (int d = 0; d < width; d++) dot = fmaf(qs[d], to_float(key[d]), dot);
+      s = dot * scale;
+    }
+    row_offset[tid] = valid ? offset : -1;
+    const float c_max = block_max(s, scratch);
+    const float m_new = fmaxf(m_run, c_max);
+    const float e = valid ? expf(s - m_new) : 0.f;
+    probs[tid] = e;
+    const float c_sum = block_sum(e, scratch);
+    const float alpha = (m_run == -INFINITY) ? 0.f : expf(m_run - m_new);
+    l_run = l_run * alpha + c_sum;
+    const int count = min(CHUNK, pos - base + 1);
+#pragma unroll
+    for (int i = 0; i < MAX_V; i++) {
+      const int d = tid + i * CHUNK;
+      if (d < rank) {
+        float a = acc[i] * alpha;
+        for (int j = 0; j < count; j++) {
+          const long long off = row_offset[j];
+          if (off >= 0) a = fmaf(probs[j], to_float(cache[off + d]), a);
+        }
+        acc[i] = a;
+      }
+    }
+    m_run = m_new;
+    __syncthreads();
+  }
+  T* dst = out + ((size_t)t * heads + h) * rank;
+#pragma unroll
+  for (int i = 0; i < MAX_V; i++) {
+    const int d = tid + i * CHUNK;
+    if (d < rank) dst[d] = from_float<T>(acc[i] / l_run);
+  }
+}
+
+// ---------------------------------------------------------------- depth_average
+// history [entries, rows, width] float32.  history[n + 1] = x; x = sum_{j <= n + 1} w[j] * history[j].
+__global__ void depth_average_kernel(float* __restrict__ history, float* __restrict__ x, const float* __restrict__ w,
+                                     int n, long long plane) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < plane; i += (long long)gridDim.x * blockDim.x) {
+    const float latest = x[i];
+    history[(long long)(n + 1) * plane + i] = latest;
+    float sum = 0.f;
+    for (int j = 0; j <= n; j++) sum = fmaf(w[j], history[(long long)j * plane + i], sum);
+    x[i] = fmaf(w[n + 1], latest, sum);
+  }
+}
+
+__global__ void softcap_kernel(float* __restrict__ x, float cap, long long count) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x)
+    x[i] = cap * tanhf(x[i] / cap);
+}
+
+inline int flat_grid(long long count, int threads) {
+  long long blocks = (count + threads - 1) / threads;
+  const long long cap = (long long)sprout_sm_count() * 16;
+  return (int)(blocks < 1 ? 1 : blocks > cap ? cap : blocks);
+}
+
+}  // namespace
+
+SPROUT_API int sprout_scale_cast(const float* x, float* y, void* h, int h_dtype, float alpha, long long count,
+                                 cudaStream_t stream) {
+  SPROUT_REQUIRE(x && y && count > 0, "scale_cast: null pointer or no elements");
+  if (h && h_dtype == SPROUT_BF16)
+    sprout_launch(scale_cast_kernel<__nv_bfloat16>, dim3(flat_grid(count, 256)), dim3(256), 0, stream, x, y, (__nv_bfloat16*)h, alpha, count);
+  else
+    sprout_launch(scale_cast_kernel<float>, dim3(flat_grid(count, 256)), dim3(256), 0, stream, x, y, (float*)h, alpha, count);
+  return sprout_check_launch("scale_cast");
+}
+
+SPROUT_API int sprout_sum_norm(const float* y, const float* gain, float* x, float* y2, void* h, int h_dtype, int rows,
+                               int hidden, float eps, float alpha, cudaStream_t stream) {
+  SPROUT_REQUIRE(y && gain && x && rows > 0 && hidden > 0, "sum_norm: null pointer or empty");
+  if (h && h_dtype == SPROUT_BF16)
+    sprout_launch(sum_norm_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, stream, y, gain, x, y2, (__nv_bfloat16*)h, hidden, eps, alpha);
+  else
+    sprout_launch(sum_norm_kernel<float>, dim3(rows), dim3(256), 0, stream, y, gain, x, y2, (float*)h, hidden, eps, alpha);
+  return sprout_check_launch("sum_norm");
+}
+
+SPROUT_API int sprout_polynorm(const void* z, int z_dtype, void* out, int out_dtype, const float* coef, int rows, int width,
+                               float eps, cudaStream_t stream) {
+  SPROUT_REQUIRE(z && out && coef && rows > 0 && width > 0, "polynorm: null pointer or empty");
+  if (z_dtype == SPROUT_F32 && out_dtype == SPROUT_F32)
+    sprout_launch(polynorm_kernel<float, float>, dim3(rows), dim3(256), 0, stream, (const float*)z, (float*)out, coef, width, eps);
+  else if (z_dtype == SPROUT_F32 && out_dtype == SPROUT_BF16)
+    sprout_launch(polynorm_kernel<float, __nv_bfloat16>, dim3(rows), dim3(256), 0, stream, (const float*)z, (__nv_bfloat16*)out, coef, width, eps);
+  else if (z_dtype == SPROUT_BF16 && out_dtype == SPROUT_BF16)
+    sprout_launch(polynorm_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(rows), dim3(256), 0, stream, (const __nv_bfloat16*)z, (__nv_bfloat16*)out, coef, width, eps);
+  else
+    return sprout_fail("polynorm: unsupported dtypes z=%d out=%d", z_dtype, out_dtype);
+  return sprout_check_launch("polynorm");
+}
+
+SPROUT_API int sprout_latent_kv_append(const float* src, int ld, const float* weight, const int* positions,
+                                       const int* seq_of_token, const int* block_table, int table_stride,
+                                       const float* cos_table, const float* sin_table, int table_positions,
+                                       int rotary_dim, int interleaved, void* cache, int cache_dtype, int tokens,
+                                       int rank, int rot, int page_tokens, int num_pages, float eps, int* status,
+                                       cudaStream_t stream) {
+  SPROUT_REQUIRE(src && weight && positions && seq_of_token && block_table && cache && status, "latent_kv_append: null pointer");
+  SPROUT_REQUIRE(tokens > 0 && rank > 0 && rot >= 0 && ld >= rank + rot && page_tokens > 0 && num_pages > 0,
+                 "latent_kv_append: sizes do not fit");
+  SPROUT_REQUIRE(rotary_dim >= 0 && rotary_dim % 2 == 0 && rotary_dim <= rot && (rotary_dim == 0 || (cos_table && sin_table)),
+                 "latent_kv_append: the rotated width must be even, at most the key part's width, and come with tables");
+  if (cache_dtype == SPROUT_F32)
+    sprout_launch(latent_kv_append_kernel<float>, dim3(tokens), dim3(128), 0, stream, src, ld, weight, positions, seq_of_token,
+                  block_table, table_stride, cos_table, sin_table, table_positions, rotary_dim, interleaved, (float*)cache,
+                  rank, rot, page_tokens, num_pages, eps, status);
+  else if (cache_dtype == SPROUT_BF16)
+    sprout_launch(latent_kv_append_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), 0, stream, src, ld, weight, positions,
+                  seq_of_token, block_table, table_stride, cos_table, sin_table, table_positions, rotary_dim, interleaved,
+                  (__nv_bfloat16*)cache, rank, rot, page_tokens, num_pages, eps, status);
+  else
+    return sprout_fail("latent_kv_append: unknown dtype %d", cache_dtype);
+  return sprout_check_launch("latent_kv_append");
+}
+
+SPROUT_API int sprout_latent_query_tail(const void* q, void* qlat, int dtype, const int* positions, const float* cos_table,
+                                        const float* sin_table, int table_positions, int rotary_dim, int interleaved,
+                                        int tokens, int heads, int dim, int rot, int rank, int* status, cudaStream_t stream) {
+  SPROUT_REQUIRE(q && qlat && positions && status && tokens > 0 && heads > 0 && dim >= 0 && rot >= 0 && rank > 0,
+                 "latent_query_tail: null pointer or sizes");
+  SPROUT_REQUIRE(rotary_dim >= 0 && rotary_dim % 2 == 0 && rotary_dim <= rot && (rotary_dim == 0 || (cos_table && sin_table)),
+                 "latent_query_tail: the rotated width must be even, at most the rotated part's width, and come with tables");
+  if (rot == 0) return 0;
+  if (dtype == SPROUT_F32)
+    sprout_launch(latent_query_tail_kernel<float>, dim3(tokens), dim3(128), 0, stream, (const float*)q, (float*)qlat, positions,
+                  cos_table, sin_table, table_positions, rotary_dim, interleaved, heads, dim, rot, rank, status);
+  else if (dtype == SPROUT_BF16)
+    sprout_launch(latent_query_tail_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), 0, stream, (const __nv_bfloat16*)q,
+                  (__nv_bfloat16*)qlat, positions, cos_table, sin_table, table_positions, rotary_dim, interleaved, heads, dim,
+                  rot, rank, status);
+  else
+    return sprout_fail("latent_query_tail: unknown dtype %d", dtype);
+  return sprout_check_launch("latent_query_tail");
+}
+
+SPROUT_API int sprout_headwise_gemm(const void* a, long long a_row, long long a_head, const void* w, void* out,
+                                    long long o_row, long long o_head, int dtype, int rows, int heads, int n, int k,
+                                    cudaStream_t stream) {
+  SPROUT_REQUIRE(a && w && out && rows > 0 && heads > 0 && n > 0 && k > 0, "headwise_gemm: null pointer or sizes");
+  SPROUT_REQUIRE(heads <= 65535 && (rows + HB - 1) / HB <= 65535, "headwise_gemm: too many heads or rows");
+  dim3 grid((n + HB - 1) / HB, (rows + HB - 1) / HB, heads);
+  if (dtype == SPROUT_F32)
+    sprout_launch(headwise_gemm_kernel<float>, grid, dim3(HTHREADS), 0, stream, (const float*)a, a_row, a_head, (const float*)w,
+                  (float*)out, o_row, o_head, rows, n, k);
+  else if (dtype == SPROUT_BF16)
+    sprout_launch(headwise_gemm_kernel<__nv_bfloat16>, grid, dim3(HTHREADS), 0, stream, (const __nv_bfloat16*)a, a_row, a_head,
+                  (const __nv_bfloat16*)w, (__nv_bfloat16*)out, o_row, o_head, rows, n, k);
+  else
+    return sprout_fail("headwise_gemm: unknown dtype %d", dtype);
+  return sprout_check_launch("headwise_gemm");
+}
+
+SPROUT_API int sprout_latent_attention_simple(const void* qlat, const void* cache, const int* block_table, int table_stride,
+                                              const int* seq_of_token, const int* positions, const float* sink, void* out,
+                                              int dtype, int tokens, int heads, int width, int rank, int page_tokens,
+                                              int num_pages, float scale, int* status, cudaStream_t stream) {
+  SPROUT_REQUIRE(qlat && cache && block_table && seq_of_token && positions && out && status, "latent_attention_simple: null pointer");
+  SPROUT_REQUIRE(tokens > 0 && heads > 0 && heads <= 65535 && rank > 0 && width >= rank && page_tokens > 0 && num_pages > 0,
+                 "latent_attention_simple: sizes do not fit");
+  SPROUT_REQUIRE(rank <= MAX_V * CHUNK, "latent_attention_simple: latent size %d above %d", rank, MAX_V * CHUNK);
+  const size_t smem = (size_t)(width + (width & 1) + CHUNK + 34) * sizeof(float) + CHUNK * sizeof(long long);
+  dim3 grid(tokens, heads);
+  if (dtype == SPROUT_F32)
+    sprout_launch(latent_attention_simple_kernel<float>, grid, dim3(CHUNK), smem, stream, (const float*)qlat, (const float*)cache,
+                  block_table, table_stride, seq_of_token, positions, sink, (float*)out, heads, width, rank, page_tokens,
+                  num_pages, scale, status);
+  else if (dtype == SPROUT_BF16)
+    sprout_launch(latent_attention_simple_kernel<__nv_bfloat16>, grid, dim3(CHUNK), smem, stream, (const __nv_bfloat16*)qlat,
+                  (const __nv_bfloat16*)cache, block_table, table_stride, seq_of_token, positions, sink, (__nv_bfloat16*)out,
+                  heads, width, rank, page_tokens, num_pages, scale, status);
+  else
+    return sprout_fail("latent_attention_simple: unknown dtype %d", dtype);
+  return sprout_check_launch("latent_attention_simple");
+}
+
+SPROUT_API int sprout_depth_average(float* history, float* x, const float* weights, int n, long long plane, cudaStream_t stream) {
+  SPROUT_REQUIRE(history && x && weights && n >= 0 && plane > 0, "depth_average: null pointer or sizes");
+  sprout_launch(depth_average_kernel, dim3(flat_grid(plane, 256)), dim3(256), 0, stream, history, x, weights, n, plane);
+  return sprout_check_launch("depth_average");
+}
+
+SPROUT_API int sprout_softcap(float* x, float cap, long long count, cudaStream_t stream) {
+  SPROUT_REQUIRE(x && count > 0 && cap > 0.f, "softcap: null pointer, no elements or a cap that is not positive");
+  sprout_launch(softcap_kernel, dim3(flat_grid(count, 256)), dim3(256), 0, stream, x, cap, count);
+  return sprout_check_launch("softcap");
+}

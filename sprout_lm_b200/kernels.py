@@ -27,7 +27,7 @@ class KernelError(RuntimeError):
     pass
 
 
-_P, _I, _F = c_void_p, c_int, c_float
+_P, _I, _F, _L = c_void_p, c_int, c_float, ctypes.c_longlong
 _SIGNATURES = {
     "sprout_embed": [_P, _I, _P, _P, _I, _I, _I, _P, _P],
     "sprout_rmsnorm": [_P, _P, _P, _I, _P, _I, _I, _F, _P],
@@ -51,6 +51,15 @@ _SIGNATURES = {
     "sprout_wait_probe": [_P, _P],
     "sprout_linear_decode": [_P, _I, _P, _P, _F, _P, _P, _I, _I, _I, _I, _P, _P],
     "sprout_linear_decode_supported": [_I, _I, _I],
+    "sprout_scale_cast": [_P, _P, _P, _I, _F, _L, _P],
+    "sprout_sum_norm": [_P, _P, _P, _P, _P, _I, _I, _I, _F, _F, _P],
+    "sprout_polynorm": [_P, _I, _P, _I, _P, _I, _I, _F, _P],
+    "sprout_latent_kv_append": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P],
+    "sprout_latent_query_tail": [_P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "sprout_headwise_gemm": [_P, _L, _L, _P, _P, _L, _L, _I, _I, _I, _I, _I, _P],
+    "sprout_latent_attention_simple": [_P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P],
+    "sprout_depth_average": [_P, _P, _P, _I, _L, _P],
+    "sprout_softcap": [_P, _F, _L, _P],
 }
 
 _lock = threading.Lock()
@@ -849,6 +858,140 @@ def feed_tokens(token_ids, rows, fed, vocab: int):
         raise KernelError("feed_tokens: one row index per token")
     _run("sprout_feed_tokens", _ptr(token_ids, "token_ids", torch.int32), _ptr(rows, "rows", torch.int32),
          _ptr(fed, "fed", torch.int32), token_ids.numel(), fed.numel(), vocab, _stream())
+
+
+# ---------------------------------------------------------------------------------- sum-then-norm streams, latent attention
+
+def scale_cast(x, y, h, alpha: float):
+    """y = alpha * x (float32) and, when ``h`` is given, h = x in h's dtype."""
+    if not (x.is_contiguous() and y.is_contiguous()) or x.shape != y.shape or (h is not None and (h.shape != x.shape or not h.is_contiguous())):
+        raise KernelError("scale_cast: x, y and h must be contiguous and of one shape")
+    _run("sprout_scale_cast", _ptr(x, "x", torch.float32), _ptr(y, "y", torch.float32), _ptr(h, "h", allow_none=True),
+         _dtype_code(h.dtype) if h is not None else F32, float(alpha), x.numel(), _stream())
+
+
+def sum_norm(y, gain, x, eps: float, y2=None, h=None, alpha: float = 1.0):
+    """x = rmsnorm(y) * gain (float32; ``x`` may be ``y``); optionally y2 = alpha * x (may be ``y``)
+    and h = x in h's dtype, for the sublayer that follows."""
+    if y.dim() != 2 or not y.is_contiguous() or not x.is_contiguous() or x.shape != y.shape or gain.numel() != y.shape[1]:
+        raise KernelError("sum_norm: y and x must be contiguous [rows, hidden], gain [hidden]")
+    for name, t in (("y2", y2), ("h", h)):
+        if t is not None and (t.shape != y.shape or not t.is_contiguous()):
+            raise KernelError(f"sum_norm: {name} must be contiguous and have y's shape")
+    _run("sprout_sum_norm", _ptr(y, "y", torch.float32), _ptr(gain, "gain", torch.float32), _ptr(x, "x", torch.float32),
+         _ptr(y2, "y2", torch.float32, True), _ptr(h, "h", allow_none=True), _dtype_code(h.dtype) if h is not None else F32,
+         y.shape[0], y.shape[1], float(eps), float(alpha), _stream())
+
+
+def polynorm(z, out, coefficients, eps: float):
+    """out = a N(z) + b N(z^2) + c N(z^3) + e per row, N(v) = v / sqrt(mean(v^2) + eps);
+    ``coefficients`` is a float32 device tensor (a, b, c, e)."""
+    if z.dim() != 2 or not z.is_contiguous() or not out.is_contiguous() or out.shape != z.shape or coefficients.numel() != 4:
+        raise KernelError("polynorm: z and out must be contiguous [rows, width], four coefficients")
+    _run("sprout_polynorm", _ptr(z, "z"), _dtype_code(z.dtype), _ptr(out, "out"), _dtype_code(out.dtype),
+         _ptr(coefficients, "coefficients", torch.float32), z.shape[0], z.shape[1], float(eps), _stream())
+
+
+def _rotary(cos_table, sin_table, limit: int, name: str):
+    if (cos_table is None) != (sin_table is None):
+        raise KernelError(f"{name}: cos and sin tables go together")
+    if cos_table is None:
+        return None, None, 0, 0
+    if cos_table.shape != sin_table.shape or cos_table.dim() != 2 or not 0 < 2 * cos_table.shape[1] <= limit \
+            or not cos_table.is_contiguous() or not sin_table.is_contiguous():
+        raise KernelError(f"{name}: cos/sin tables must be contiguous [max_positions, rotary_dim / 2] with rotary_dim <= {limit}")
+    return _ptr(cos_table, "cos", torch.float32), _ptr(sin_table, "sin", torch.float32), cos_table.shape[0], 2 * cos_table.shape[1]
+
+
+def latent_kv_append(src, weight, positions, seq_of_token, block_table, cos_table, sin_table, interleaved, cache, rank: int,
+                     eps: float, status):
+    """Row t of ``src`` (float32 [tokens, >= rank + rot], unit inner stride) is [latent | shared key part]:
+    the latent is RMS-normed and multiplied by ``weight``, the key part's first ``rotary_dim`` elements
+    are rotated by the token's position, and the row is stored in ``cache``
+    [pages, 1, page_tokens, rank + rot] at the token's place."""
+    _rows_contiguous(src, "src")
+    _rows_contiguous(block_table, "block_table")
+    if cache.dim() != 4 or cache.shape[1] != 1 or not cache.is_contiguous() or cache.shape[3] < rank:
+        raise KernelError("latent_kv_append: the cache must be contiguous [pages, 1, page_tokens, rank + rot]")
+    rot = cache.shape[3] - rank
+    T = src.shape[0]
+    if src.shape[1] < rank + rot or weight.numel() != rank or positions.numel() != T or seq_of_token.numel() != T:
+        raise KernelError("latent_kv_append: shapes do not fit")
+    cos, sin, table_positions, rotary_dim = _rotary(cos_table, sin_table, max(rot, 1), "latent_kv_append")
+    _run("sprout_latent_kv_append", _ptr(src, "src", torch.float32), src.stride(0), _ptr(weight, "weight", torch.float32),
+         _ptr(positions, "positions", torch.int32), _ptr(seq_of_token, "seq_of_token", torch.int32),
+         _ptr(block_table, "block_table", torch.int32), block_table.stride(0), cos, sin, table_positions, rotary_dim,
+         1 if interleaved else 0, _ptr(cache, "cache"), _dtype_code(cache.dtype), T, rank, rot, cache.shape[2], cache.shape[0],
+         float(eps), _ptr(status, "status", torch.int32), _stream())
+
+
+def latent_query_tail(q, qlat, positions, cos_table, sin_table, interleaved, heads: int, dim: int, rot: int, rank: int, status):
+    """qlat[t, h, rank:] = q[t, h, dim:] with its first ``rotary_dim`` elements rotated by the token's position;
+    q is [tokens, heads * (dim + rot)], qlat [tokens, heads * (rank + rot)]."""
+    T = q.shape[0]
+    if not q.is_contiguous() or not qlat.is_contiguous() or q.dtype != qlat.dtype or tuple(q.shape) != (T, heads * (dim + rot)) \
+            or tuple(qlat.shape) != (T, heads * (rank + rot)) or positions.numel() != T:
+        raise KernelError("latent_query_tail: shapes do not fit")
+    cos, sin, table_positions, rotary_dim = _rotary(cos_table, sin_table, max(rot, 1), "latent_query_tail")
+    _run("sprout_latent_query_tail", _ptr(q, "q"), _ptr(qlat, "qlat"), _dtype_code(q.dtype), _ptr(positions, "positions", torch.int32),
+         cos, sin, table_positions, rotary_dim, 1 if interleaved else 0, T, heads, dim, rot, rank,
+         _ptr(status, "status", torch.int32), _stream())
+
+
+def headwise_gemm(a, weight, out, heads: int, a_head_stride: int, out_head_stride: int):
+    """out[t, h, :n] = weight[h] @ a[t, h, :k] for every head: ``weight`` is contiguous [heads, n, k];
+    head h's input starts at column h * a_head_stride of ``a``'s rows, its output at column
+    h * out_head_stride of ``out``'s rows.  float32 accumulation in ascending k."""
+    _rows_contiguous(a, "a")
+    _rows_contiguous(out, "out")
+    if weight.dim() != 3 or weight.shape[0] != heads or not weight.is_contiguous() or a.dtype != weight.dtype or out.dtype != a.dtype:
+        raise KernelError("headwise_gemm: weight must be contiguous [heads, n, k] of the activations' dtype")
+    n, k = weight.shape[1], weight.shape[2]
+    if a.shape[0] != out.shape[0] or (heads - 1) * a_head_stride + k > a.shape[1] or (heads - 1) * out_head_stride + n > out.shape[1]:
+        raise KernelError("headwise_gemm: the heads do not fit the rows")
+    _run("sprout_headwise_gemm", _ptr(a, "a"), a.stride(0), a_head_stride, _ptr(weight, "weight"), _ptr(out, "out"), out.stride(0),
+         out_head_stride, _dtype_code(a.dtype), a.shape[0], heads, n, k, _stream())
+
+
+def latent_attention_simple(qlat, cache, block_table, seq_of_token, positions, sink, out, heads: int, rank: int, scale: float, status):
+    """Causal attention of every (token, head) row of ``qlat`` [tokens, heads * width] over the rows of
+    its request in ``cache`` [pages, 1, page_tokens, width]: score = scale * (row . key row), value = the
+    key row's first ``rank`` elements; ``sink`` (float32 [heads] or None) adds exp(sink[h]) to the softmax
+    denominator.  out [tokens, heads * rank].  float32 arithmetic; the true 32-bit path."""
+    T = qlat.shape[0]
+    width = cache.shape[3]
+    if cache.dim() != 4 or cache.shape[1] != 1 or not cache.is_contiguous() or cache.dtype != qlat.dtype or out.dtype != qlat.dtype \
+            or not qlat.is_contiguous() or not out.is_contiguous() or tuple(qlat.shape) != (T, heads * width) \
+            or tuple(out.shape) != (T, heads * rank) or (sink is not None and sink.numel() != heads):
+        raise KernelError("latent_attention_simple: shapes or dtypes do not fit")
+    _rows_contiguous(block_table, "block_table")
+    _run("sprout_latent_attention_simple", _ptr(qlat, "qlat"), _ptr(cache, "cache"), _ptr(block_table, "block_table", torch.int32),
+         block_table.stride(0), _ptr(seq_of_token, "seq_of_token", torch.int32), _ptr(positions, "positions", torch.int32),
+         _ptr(sink, "sink", torch.float32, True), _ptr(out, "out"), _dtype_code(qlat.dtype), T, heads, width, rank,
+         cache.shape[2], cache.shape[0], float(scale), _ptr(status, "status", torch.int32), _stream())
+
+
+def latent_attention(qlat, cache, ctx, sink, out, heads: int, rank: int, scale: float, status):
+    """Latent attention of the step's rows over their requests' pages (``cache`` is a CacheView whose
+    key buffer holds the rows): picks the kernel for the dtype and the step's shape."""
+    latent_attention_simple(qlat, cache.k, cache.block_table, ctx.seq_of_token, ctx.positions, sink, out, heads, rank, scale, status)
+
+
+def depth_average(history, x, weights, n: int):
+    """history[n + 1] = x, then x = sum over j <= n + 1 of weights[j] * history[j]; history is float32
+    [entries, rows, width], x float32 [rows, width], weights float32 with at least n + 2 entries."""
+    if history.dim() != 3 or not history.is_contiguous() or not x.is_contiguous() or tuple(history.shape[1:]) != tuple(x.shape) \
+            or not 0 <= n + 1 < history.shape[0] or weights.numel() < n + 2:
+        raise KernelError("depth_average: shapes do not fit")
+    _run("sprout_depth_average", _ptr(history, "history", torch.float32), _ptr(x, "x", torch.float32),
+         _ptr(weights, "weights", torch.float32), int(n), x.numel(), _stream())
+
+
+def softcap(x, cap: float):
+    """x = cap * tanh(x / cap) in place (float32)."""
+    if not x.is_contiguous():
+        raise KernelError("softcap: x must be contiguous")
+    _run("sprout_softcap", _ptr(x, "x", torch.float32), float(cap), x.numel(), _stream())
 
 
 def describe_status(word: int) -> str:

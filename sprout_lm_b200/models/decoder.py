@@ -30,12 +30,13 @@ class DecoderModel:
         self.blocks = [build_block(layer) for layer in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm)
         self.head = build_part("head", spec.head)
+        self.stream = build_part("stream", spec.stream) if spec.stream is not None else None
         self.runtime: Runtime | None = None
         self._decode_plans: dict = {}
 
     # ------------------------------------------------------------------ weights
     def parts(self):
-        return [self.embedding, *self.blocks, self.final_norm, self.head]
+        return [self.embedding, *self.blocks, self.final_norm, self.head, *([self.stream] if self.stream else [])]
 
     def tensor_decls(self):
         decls, seen = [], set()
@@ -110,10 +111,13 @@ class DecoderModel:
         [len(ctx.logits_rows), vocab], or None when no logits are wanted.  ``storage`` is the device side of the cache
         (``cache.storage.CacheStorage``)."""
         x = self.embedding.forward(ctx.token_ids)
-        for call in self.spec.order:
+        carry = self.stream.begin(x, len(self.spec.order)) if self.stream else None
+        for n, call in enumerate(self.spec.order):
             cache = storage.view(call.cache, ctx, write=call.writes_cache)
             state = storage.state_view(call.layer, ctx)
             self.blocks[call.layer].forward(x, ctx, cache, state)
+            if self.stream:
+                self.stream.after(carry, n, x)
         if ctx.logits_rows.numel() == 0:
             return None             # nothing wanted: the layers have filled the cache, the head is skipped
         return self.head.forward(self.final_norm.forward(x, rows=ctx.logits_rows))

@@ -24,6 +24,9 @@ Categories and what each must provide:
                      ``forward(x, ctx, cache, state)``.
 * ``embedding``:     ``forward(token_ids) -> x`` (float32 [tokens, hidden]).
 * ``head``:          ``forward(h) -> logits`` (float32 [rows, vocab]).
+* ``stream``:        what goes from one layer call to the next when that is more than the layer's
+                     result: ``begin(x, calls) -> carry`` after the embedding, ``after(carry, n, x)``
+                     after the n-th call of the run order (replaces ``x`` in place).
 
 ``ctx`` is the step's batch on the device (``engine.batch.StepContext``); ``cache`` a
 ``CacheView`` of the cache slot the call reads (and writes); ``state`` a ``StateView`` or None.
@@ -37,7 +40,7 @@ import torch
 
 from ..config.specs import ConfigError, PartSpec
 
-CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head")
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head", "stream")
 _REGISTRY: dict[str, dict[str, type]] = {c: {} for c in CATEGORIES}
 
 
@@ -70,7 +73,8 @@ def registered_parts(category: str) -> tuple[str, ...]:
 @dataclass(frozen=True)
 class TensorDecl:
     """A checkpoint tensor that a part reads.  ``init`` tells the random-weights mode how to
-    fill it: ``matrix`` and ``bias`` are N(0, 0.02), ``gain`` is 1 + N(0, 0.02)."""
+    fill it: ``matrix`` and ``bias`` are N(0, 0.02), ``gain`` is 1 + N(0, 0.02); ``pass_last`` and
+    ``polynomial`` are described in ``weights.random_init``."""
     name: str
     shape: tuple[int, ...]
     init: str = "matrix"
@@ -79,11 +83,18 @@ class TensorDecl:
 @dataclass(frozen=True)
 class CacheSpec:
     """What a mixer keeps per token: keys and values of ``kv_heads`` heads of ``head_dim``.
-    kind ``full`` keeps every position, ``window`` the last ``window``."""
+    kind ``full`` keeps every position, ``window`` the last ``window``.  ``value_dim`` is the width of a
+    value row when it differs from a key row's (None: ``head_dim``); 0 means the mixer keeps no values of
+    their own (it reads them out of the key rows), and the slot then has no value buffer."""
     kv_heads: int
     head_dim: int
     kind: str = "full"
     window: int | None = None
+    value_dim: int | None = None
+
+    @property
+    def value_width(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
     @property
     def group_key(self):

@@ -43,3 +43,54 @@ def build_block(layer: LayerSpec):
     except KeyError:
         raise ConfigError(f"no block arrangement {layer.block!r} is registered") from None
     return cls(prefix=layer.prefix, layer=layer)
+
+
+@register_part("block", "post_norm")
+class PostNormBlock(Part):
+    """The norm comes after the sum: x <- norm_0(alpha x + mixer(x)), then x <- norm_1(alpha x + ffn(x));
+    the sublayers read x itself.  The sums and the stream are float32; a sublayer reads x in the compute
+    dtype.  A layer without a feed-forward (``feed_forward.kind == "none"``) is the first half alone.
+
+    A sublayer gets ``h`` = x in the compute dtype and ``y`` = alpha x (float32) and adds its output to
+    y; the norm kernel that follows writes x and, for the second sublayer, the next h and y as well.
+    """
+
+    def __init__(self, prefix: str, layer: LayerSpec):
+        self.alpha = float(layer.options.get("alpha", 1.0))
+        self.has_ffn = layer.feed_forward.kind != "none"
+        if len(layer.norms) != (2 if self.has_ffn else 1):
+            raise ValueError("a post_norm block has one norm per sublayer")
+        self.norms = [build_part("norm", spec, prefix) for spec in layer.norms]
+        for norm in self.norms:
+            if getattr(norm, "fused_kind", None) != "rmsnorm":
+                raise ValueError("a post_norm block takes RMS norms")
+        self.mixer = build_part("mixer", layer.mixer, prefix)
+        self.feed_forward = build_part("feed_forward", layer.feed_forward, prefix) if self.has_ffn else None
+
+    def parts(self):
+        return [*self.norms, self.mixer, *([self.feed_forward] if self.has_ffn else [])]
+
+    def tensor_decls(self):
+        return [decl for part in self.parts() for decl in part.tensor_decls()]
+
+    def load(self, source):
+        for part in self.parts():
+            part.load(source)
+        self.dtype = source.runtime.dtype
+
+    def forward(self, x, ctx, cache, state):
+        import torch
+        from .. import kernels
+        narrow = self.dtype != torch.float32
+        y = torch.empty_like(x)
+        h = torch.empty(x.shape, dtype=self.dtype, device=x.device) if narrow else None
+        kernels.scale_cast(x, y, h, self.alpha)
+        self.mixer.forward(h if narrow else x, y, ctx, cache, state)
+        norm = self.norms[0]
+        if not self.has_ffn:
+            kernels.sum_norm(y, norm.gain, x, norm.eps)
+            return
+        kernels.sum_norm(y, norm.gain, x, norm.eps, y2=y, h=h, alpha=self.alpha)
+        self.feed_forward.forward(h if narrow else x, y, ctx)
+        norm = self.norms[1]
+        kernels.sum_norm(y, norm.gain, x, norm.eps)

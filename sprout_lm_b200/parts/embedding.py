@@ -1,5 +1,6 @@
 """Token embedding (a row copy, no scaling: src/qwen.ts:162-163) and the output head
-(logits = W h, no bias; W is the embedding matrix itself when tied: src/qwen.ts:152,203)."""
+(logits = W h, no bias; W is the embedding matrix itself when tied: src/qwen.ts:152,203).
+With ``softcap`` the head's logits become softcap * tanh(logits / softcap)."""
 from __future__ import annotations
 
 import torch
@@ -11,9 +12,9 @@ from .linear import Linear
 
 @register_part("embedding", "token_embedding")
 class TokenEmbedding(Part):
-    def __init__(self, prefix: str, vocab_size: int, hidden_size: int, name: str = "embed_tokens"):
+    def __init__(self, prefix: str, vocab_size: int, hidden_size: int, name: str = "embed_tokens", suffix: str = ".weight"):
         self.vocab_size, self.hidden_size = vocab_size, hidden_size
-        self.tensor_name = f"{prefix}{name}.weight"
+        self.tensor_name = f"{prefix}{name}{suffix}"
         self.table = None
         self.runtime = None
 
@@ -33,9 +34,14 @@ class TokenEmbedding(Part):
 @register_part("head", "lm_head")
 class LMHead(Part):
     def __init__(self, prefix: str, vocab_size: int, hidden_size: int, tied_to: str | None = None,
-                 name: str = "lm_head"):
+                 name: str = "lm_head", suffix: str = ".weight", softcap: float | None = None,
+                 any_inner_size: bool = False):
+        if softcap is not None and not softcap > 0:
+            raise ValueError("lm_head: softcap must be positive")
         self.vocab_size, self.hidden_size = vocab_size, hidden_size
-        self.tensor_name = f"{prefix}{tied_to or name}.weight"
+        self.softcap = None if softcap is None else float(softcap)
+        self.any_inner_size = any_inner_size
+        self.tensor_name = f"{prefix}{tied_to or name}{suffix}"
         self.tied = tied_to is not None
         self.linear = None
 
@@ -43,7 +49,10 @@ class LMHead(Part):
         return [] if self.tied else [TensorDecl(self.tensor_name, (self.vocab_size, self.hidden_size))]
 
     def load(self, source: WeightSource):
-        self.linear = Linear(source.matrix(self.tensor_name), None, source.runtime.status)
+        self.linear = Linear(source.matrix(self.tensor_name), None, source.runtime.status, any_inner_size=self.any_inner_size)
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
-        return self.linear.forward(h, out_dtype=torch.float32)
+        logits = self.linear.forward(h, out_dtype=torch.float32)
+        if self.softcap is not None:
+            kernels.softcap(logits, self.softcap)
+        return logits

@@ -33,18 +33,21 @@ def small_batch_split_k(out_features: int, in_features: int, tokens: int, residu
 
 
 class Linear:
-    def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None, status: torch.Tensor):
+    def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None, status: torch.Tensor, any_inner_size: bool = False):
         self.weight = weight
         self.bias = bias
         self.status = status
         self.out_features, self.in_features = weight.shape
         self.sms = kernels.sm_count(weight.device) if weight.is_cuda else 0
-        if weight.dtype == torch.bfloat16 and self.in_features % 8:
+        # bfloat16 rows that do not start on 16-byte boundaries cannot be fetched by TMA: such a matrix is
+        # refused, or with ``any_inner_size`` runs ``forward`` on the CUDA-core product (float32 accumulation)
+        if weight.dtype == torch.bfloat16 and self.in_features % 8 and not any_inner_size:
             raise ValueError(f"a bfloat16 matrix needs an inner size that is a multiple of 8 (got {self.in_features}): "
                              "its rows must start on 16-byte boundaries")
+        self.tensor_cores = weight.dtype == torch.bfloat16 and self.in_features % 8 == 0
         # A handful of tokens through a small matrix: the light kernel (csrc/linear_decode.cu)
         self.small_tokens = 0
-        if weight.dtype == torch.bfloat16 and weight.is_cuda and small_batch_enabled():
+        if self.tensor_cores and weight.is_cuda and small_batch_enabled():
             for tokens in (SMALL_BATCH_TOKENS, 8):       # two tiles of 8 tokens where the pieces leave room, else one
                 if kernels.linear_decode_supported(tokens, self.out_features, self.in_features):
                     self.small_tokens = tokens
@@ -110,7 +113,7 @@ class Linear:
             out = residual
         else:
             out = torch.empty((a.shape[0], self.out_features), dtype=out_dtype or a.dtype, device=a.device)
-        if self.weight.dtype == torch.bfloat16:
+        if self.tensor_cores and a.stride(0) % 8 == 0:
             if residual is not None and self.bias is None and a.shape[0] <= self.small_tokens:
                 kernels.linear_decode(self.weight, out, self.status, a=a)
                 return out

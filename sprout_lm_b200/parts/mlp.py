@@ -75,3 +75,34 @@ class SwiGLUMLP(Part):
             return False
         kernels.ffn_decode(x, norm.gain, norm.eps, self.gate_up.weight, self.down.weight, self.gate_up.status)
         return True
+
+
+@register_part("feed_forward", "polynorm_mlp")
+class PolyNormMLP(Part):
+    """x += W_down act(W_up h) with act(z) = a N(z) + b N(z^2) + c N(z^3) + e: powers element by element,
+    N divides a token's vector by its root mean square (eps inside the root), and (a, b, c, e) is a
+    learned tensor of four numbers.  The up product's output and the three means are float32."""
+
+    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, eps: float, names: dict | None = None):
+        if hidden_size <= 0 or intermediate_size <= 0 or eps <= 0:
+            raise ValueError("polynorm_mlp: sizes and eps must be positive")
+        self.hidden_size, self.intermediate_size, self.eps = hidden_size, intermediate_size, float(eps)
+        names = names or {"up": "up.weight", "down": "down.weight", "act": "act"}
+        self.names = {key: prefix + value for key, value in names.items()}
+        self.up = self.down = self.coefficients = None
+
+    def tensor_decls(self):
+        return [TensorDecl(self.names["up"], (self.intermediate_size, self.hidden_size)),
+                TensorDecl(self.names["down"], (self.hidden_size, self.intermediate_size)),
+                TensorDecl(self.names["act"], (4,), "polynomial")]
+
+    def load(self, source: WeightSource):
+        self.up = Linear(source.matrix(self.names["up"]), None, source.runtime.status, any_inner_size=True)
+        self.down = Linear(source.matrix(self.names["down"]), None, source.runtime.status, any_inner_size=True)
+        self.coefficients = source.vector(self.names["act"])
+
+    def forward(self, h, x, ctx=None):
+        z = self.up.forward(h, out_dtype=torch.float32)
+        act = torch.empty(z.shape, dtype=h.dtype, device=h.device)
+        kernels.polynorm(z, act, self.coefficients, self.eps)
+        self.down.forward(act, residual=x)

@@ -1,4 +1,8 @@
-"""Learned RMSNorm: out = fround(x / sqrt(mean(x^2) + eps)) * gain (src/qwen.ts:72-77)."""
+"""Learned RMSNorm: out = fround(x / sqrt(mean(x^2) + eps)) * gain (src/qwen.ts:72-77).
+
+``offset`` is added to the stored weight to give the gain: 0 for a weight stored around one, 1 for a
+weight stored around zero (gain = 1 + w).  ``suffix`` is what follows the part's name in the
+checkpoint's tensor name."""
 from __future__ import annotations
 
 import torch
@@ -11,19 +15,21 @@ from .base import Part, TensorDecl, WeightSource, register_part
 class RMSNorm(Part):
     fused_kind = "rmsnorm"       # a consumer that has this norm's arithmetic in its own kernel may take gain and eps
 
-    def __init__(self, prefix: str, size: int, eps: float, name: str = "norm"):
+    def __init__(self, prefix: str, size: int, eps: float, name: str = "norm", offset: float = 0.0, suffix: str = ".weight"):
         if eps <= 0:
             raise ValueError("rmsnorm: eps must be positive")
-        self.size, self.eps = int(size), float(eps)
-        self.tensor_name = f"{prefix}{name}.weight"
+        self.size, self.eps, self.offset = int(size), float(eps), float(offset)
+        self.tensor_name = f"{prefix}{name}{suffix}"
         self.gain = None
         self.out_dtype = None
 
     def tensor_decls(self):
-        return [TensorDecl(self.tensor_name, (self.size,), "gain")]
+        return [TensorDecl(self.tensor_name, (self.size,), "gain" if self.offset == 0.0 else "bias")]
 
     def load(self, source: WeightSource):
         self.gain = source.vector(self.tensor_name)
+        if self.offset:
+            self.gain = (self.gain + self.offset).contiguous()
         self.out_dtype = source.runtime.dtype
 
     def forward(self, x: torch.Tensor, rows: torch.Tensor | None = None) -> torch.Tensor:
