@@ -173,7 +173,7 @@ def run_plan_in_process(runner, plan) -> dict:
 
 
 def run_plan_with_trace_run(model_dir, dtype: str, plan, out_dir, max_tokens: int, page_tokens: int = 16,
-                            extra_env=None) -> dict:
+                            extra_env=None, vocab: int | None = None) -> dict:
     """Drive bin/trace_run through a plan over its standard input; same result form."""
     import os
     lines, places_by_step, position = [], {}, {}
@@ -193,8 +193,9 @@ def run_plan_with_trace_run(model_dir, dtype: str, plan, out_dir, max_tokens: in
     done = subprocess.run(cmd, input="\n".join(lines) + "\n", capture_output=True, text=True, env=env, timeout=900)
     assert done.returncode == 0, done.stderr[-4000:]
     assert [l for l in done.stdout.splitlines() if l.startswith("done ")] == [f"done {i}" for i in range(len(plan))]
-    _, w = _plain_model(str(model_dir))
-    vocab = w["model.embed_tokens.weight"].shape[0]
+    if vocab is None:
+        _, w = _plain_model(str(model_dir))
+        vocab = w["model.embed_tokens.weight"].shape[0]
     out = {}
     for index, places in places_by_step.items():
         if not places:
