@@ -639,6 +639,176 @@ def timed_gemms(tokens: int, shape: str = "0.5b", repeats: int = 20) -> dict:
     return result
 
 
+# Tulipel (latent attention) at sizes that resemble a real model's layers, and the Qwen2 configuration of equal
+# width, heads, head size (dim + rot_dim), layers, vocabulary and feed-forward parameters beside it
+LATENT_SHAPES = {
+    "1b": dict(width=2048, heads=16, dim=64, rot_dim=64, vdim=128, kv_rank=512, q_rank=768, ff=8192, vocab=32768,
+               qwen=dict(intermediate_size=5464, num_key_value_heads=4)),
+    "0.3b": dict(width=1024, heads=8, dim=64, rot_dim=64, vdim=128, kv_rank=256, q_rank=384, ff=4096, vocab=32768,
+                 qwen=dict(intermediate_size=2736, num_key_value_heads=2)),
+}
+
+
+def latent_folders(shape: str, layers: int):
+    """(Tulipel folder, Qwen2 folder of equal size), random weights, written once."""
+    from sprout_lm_b200 import parse_config, write_random_model
+    z = LATENT_SHAPES[shape]
+    scale = (z["dim"] + z["rot_dim"]) ** -0.5
+
+    def mixer(kind, **extra):
+        rot = {"base": 10000.0, "dims": z["rot_dim"]}
+        if kind == "latent_attention_2":
+            rot["scaling"] = {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}
+        return {"type": kind, "mlp": {"kind": "dense", "ff": z["ff"]},
+                "mixer": {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot_dim"], "vdim": z["vdim"], "kv_rank": z["kv_rank"],
+                          "scale": scale, "rot": rot, **extra}}
+    entries = []
+    for i in range(layers):                       # the two kinds in turn; every fourth layer reads the rows of the one two before
+        if i % 2 == 0:
+            entries.append(mixer("latent_attention_2", **({"kv_from": i - 2} if i % 4 == 2 else {})))
+        else:
+            entries.append(mixer("latent_attention", q_rank=z["q_rank"]))
+    raw = {"architecture": "Tulipel", "vocab": z["vocab"], "width": z["width"], "postln_alpha": 2.0, "logit_softcap": 30.0,
+           "norm": {"eps": 1e-5}, "layers": entries, "max_positions": 16384}
+    qwen = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_act": "silu", "hidden_size": z["width"],
+            "num_hidden_layers": layers, "num_attention_heads": z["width"] // (z["dim"] + z["rot_dim"]), "vocab_size": z["vocab"],
+            "max_position_embeddings": 16384, "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "tie_word_embeddings": False,
+            "eos_token_id": 0, **z["qwen"]}
+    folders = []
+    for tag, config in (("tulipel", raw), ("qwen2", qwen)):
+        folder = Path(tempfile.gettempdir()) / f"sprout_lm_b200_bench_{os.getuid()}_latent_{shape}_{tag}_L{layers}"
+        if not (folder / "complete").exists():
+            print(f"[bench] writing random weights to {folder}", file=sys.stderr, flush=True)
+            write_random_model(folder, parse_config(config), seed=0)
+            (folder / "complete").write_text("ok")
+        folders.append(folder)
+    return folders[0], folders[1], raw, qwen
+
+
+def _median_us(call, repeats: int = 10) -> float:
+    import torch
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(5):
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(repeats):
+            call()
+        end.record()
+        torch.cuda.synchronize()
+        times.append(begin.elapsed_time(end) * 1000 / repeats)
+    return statistics.median(times)
+
+
+def timed_latent_kernels(shape: str, tokens: int, batch: int, context: int, peak: dict) -> dict:
+    """The new design's attention kernels alone beside the grouped-query kernels at equal heads and head size:
+    one prompt of ``tokens`` tokens (FLOPs of the causal half against the measured bf16 rate) and ``batch`` decode
+    tokens over ``context`` keys each (cache bytes read against the measured copy rate)."""
+    import torch
+    from types import SimpleNamespace
+    from sprout_lm_b200 import kernels
+    z = LATENT_SHAPES[shape]
+    heads, rank, width, page = z["heads"], z["kv_rank"], z["kv_rank"] + z["rot_dim"], 16
+    g = torch.Generator(device="cuda").manual_seed(0)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    sink = torch.zeros(heads, device="cuda")
+    out = {}
+
+    def ctx_for(requests, new, held):
+        t = requests * new
+        return SimpleNamespace(seq_of_token=torch.arange(requests, dtype=torch.int32, device="cuda").repeat_interleave(new),
+                               positions=(torch.arange(new, dtype=torch.int32, device="cuda") + (held - new)).repeat(requests),
+                               q_start=(torch.arange(requests + 1, dtype=torch.int32, device="cuda") * new),
+                               context_lens=torch.full((requests,), held, dtype=torch.int32, device="cuda"), max_q_len=new,
+                               max_context=held, planned_context=0, num_seqs=requests, num_tokens=t)
+    for label, requests, new, held in (("prefill", 1, tokens, tokens), ("decode", batch, 1, context)):
+        pages = -(-held // page)
+        table_width = -(-pages // 64) * 64
+        cache = (torch.randn(requests * pages + 1, 1, page, width, device="cuda", generator=g) * 0.3).to(torch.bfloat16)
+        table = torch.full((requests, table_width), -1, dtype=torch.int32, device="cuda")
+        table[:, :pages] = torch.randperm(requests * pages, device="cuda", generator=g).to(torch.int32).reshape(requests, pages)
+        q = (torch.randn(requests * new, heads * width, device="cuda", generator=g) * 0.3).to(torch.bfloat16)
+        o = torch.empty(requests * new, heads * rank, dtype=torch.bfloat16, device="cuda")
+        view = SimpleNamespace(k=cache, v=None, block_table=table, page_tokens=page, write=False)
+        ctx = ctx_for(requests, new, held)
+        us = _median_us(lambda: kernels.latent_attention(q, view, ctx, sink, o, heads, rank, z["dim"] ** -0.5, status),
+                        repeats=3 if label == "prefill" else 10)
+        if label == "prefill":
+            flops = 2.0 * heads * (width + rank) * tokens * (tokens + 1) / 2
+            out["latent_prefill"] = {"us": round(us, 1), "tflops": round(flops / us / 1e6, 1),
+                                     "of_measured_bf16": round(flops / us / 1e6 / peak["bf16_tflops"], 3)}
+        else:
+            mb = batch * context * width * 2 / 1e6
+            out["latent_decode"] = {"us": round(us, 1), "gbs": round(mb / us * 1e3), "mb": round(mb, 1),
+                                    "of_measured_copy": round(mb / us * 1e3 / peak["hbm_gbs"], 3)}
+    # the grouped-query kernels at equal heads and head size
+    kv_heads, head_dim = z["qwen"]["num_key_value_heads"], z["dim"] + z["rot_dim"]
+    q_heads = z["width"] // head_dim
+    pages = -(-tokens // page)
+    k = torch.randn(pages + 1, kv_heads, page, head_dim, device="cuda", generator=g).to(torch.bfloat16)
+    v = torch.randn(pages + 1, kv_heads, page, head_dim, device="cuda", generator=g).to(torch.bfloat16)
+    table = torch.randperm(pages, device="cuda", generator=g).to(torch.int32).reshape(1, pages)
+    q = torch.randn(tokens, q_heads * head_dim, device="cuda", generator=g).to(torch.bfloat16)
+    o = torch.empty_like(q)
+    q_start = torch.tensor([0, tokens], dtype=torch.int32, device="cuda")
+    positions = torch.arange(tokens, dtype=torch.int32, device="cuda")
+    variant = "tcgen05" if head_dim in (64, 128) else "mma_sync"
+    us = _median_us(lambda: kernels.attention_prefill(q, k, v, table, q_start, positions, o, q_heads, kv_heads, head_dim, status, variant=variant))
+    flops = 4.0 * q_heads * head_dim * tokens * (tokens + 1) / 2
+    out["gqa_prefill"] = {"us": round(us, 1), "tflops": round(flops / us / 1e6, 1), "variant": variant,
+                          "of_measured_bf16": round(flops / us / 1e6 / peak["bf16_tflops"], 3)}
+    table_width = -(-(-(-context // page)) // 64) * 64
+    total = batch * table_width
+    k = torch.randn(total, kv_heads, page, head_dim, device="cuda", generator=g).to(torch.bfloat16)
+    v = torch.randn(total, kv_heads, page, head_dim, device="cuda", generator=g).to(torch.bfloat16)
+    table = torch.randperm(total, device="cuda", generator=g).to(torch.int32).reshape(batch, table_width)
+    lens = torch.full((batch,), context, dtype=torch.int32, device="cuda")
+    q = torch.randn(batch, q_heads * head_dim, device="cuda", generator=g).to(torch.bfloat16)
+    o = torch.empty_like(q)
+    us = _median_us(lambda: kernels.attention_decode(q, k, v, table, lens, o, q_heads, kv_heads, head_dim, status,
+                                                     live_keys=-(-context // 128) * 128))
+    mb = 2.0 * batch * context * kv_heads * head_dim * 2 / 1e6
+    out["gqa_decode"] = {"us": round(us, 1), "gbs": round(mb / us * 1e3), "mb": round(mb, 1),
+                         "of_measured_copy": round(mb / us * 1e3 / peak["hbm_gbs"], 3)}
+    assert int(status.item()) == 0
+    return out
+
+
+def timed_latent(args) -> dict:
+    """``--only latent``: prefill and decode throughput of Tulipel at ``--shape 1b|0.3b`` (random weights,
+    ``--layers`` layers, 4 if not given) beside Qwen2 at equal size, through the same runner, and the attention
+    kernels of both alone."""
+    import numpy as np
+    import torch
+    from sprout_lm_b200 import load_model
+    from sprout_lm_b200.engine.step import ModelRunner
+    shape = args.shape if args.shape in LATENT_SHAPES else "1b"
+    layers = args.layers or 4
+    peak = peaks()
+    tulipel_dir, qwen_dir, _, _ = latent_folders(shape, layers)
+    prompt_len = args.prompt_len
+    result = {"impl": "ours", "only": "latent", "shape": shape, "layers": layers, "dtype": "bf16", "data": "synthetic",
+              "prefill_tokens": args.tokens, "decode_batch": args.batch, "decode_prompt_len": prompt_len, "steps": args.steps,
+              "peaks": {"bf16_tflops": peak["bf16_tflops"], "hbm_gbs": peak["hbm_gbs"], "source": peak.get("source", "measured")}}
+    for tag, folder in (("tulipel", tulipel_dir), ("qwen2", qwen_dir)):
+        model = load_model(folder, dtype="bfloat16", device="cuda:0")
+        slots = max(64, args.batch)
+        pages = slots * (-(-(prompt_len + args.steps + args.warmup + 16) // 16)) + args.tokens // 16 + 16
+        runner = ModelRunner(model, num_pages=pages, page_tokens=16, max_requests=slots, prefix_caching=False)
+        rng = np.random.default_rng(0)
+        ms = timed_prefill(runner, args.tokens, rng)
+        decode = timed_decode(runner, args.batch, prompt_len, args.steps, args.warmup, rng)
+        result[tag] = {"prefill_ms": round(ms, 3), "prefill_tokens_per_s": round(args.tokens / ms * 1000),
+                       "decode_ms_per_step": round(decode["ms_per_step"], 4), "decode_tokens_per_s": round(decode["tokens_per_s"]),
+                       "decode_launches_per_step": decode["launches_per_step"]}
+        del runner, model
+        torch.cuda.empty_cache()
+    result["kernels"] = timed_latent_kernels(shape, args.tokens, max(args.batch, 64), 2048, peak)
+    return result
+
+
 def run(args) -> dict:
     import numpy as np
     import torch
@@ -646,6 +816,8 @@ def run(args) -> dict:
     from sprout_lm_b200.cache.storage import cache_bytes_per_token
     from sprout_lm_b200.engine.step import ModelRunner
     kernels.load_library(verbose=True)
+    if args.only == "latent":
+        return timed_latent(args)
     if args.only == "attention":
         return timed_attention(args.tokens, args.shape)
     if args.only == "gemm":
@@ -753,9 +925,9 @@ def main() -> int:
     parser.add_argument("--portion", type=int, default=4096, help="with --only long-prompt: tokens of a step (--tokens: of the whole prompt)")
     parser.add_argument("--prompt-len", type=int, default=512, help="with --only decode: tokens of every request's prompt (the context grows to hold it)")
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
-    parser.add_argument("--only", choices=["all", "decode", "prefill", "ablate", "attention", "decode-attention", "gemm", "serve", "long-prompt"], default="all",
+    parser.add_argument("--only", choices=["all", "decode", "prefill", "ablate", "attention", "decode-attention", "gemm", "serve", "long-prompt", "latent"], default="all",
                         help="measure one part only (for profiling captures); the JSON line then holds that part")
-    parser.add_argument("--shape", choices=sorted(SHAPES), default="0.5b", help="with --only: the model's sizes")
+    parser.add_argument("--shape", choices=sorted(SHAPES) + sorted(LATENT_SHAPES), default="0.5b", help="with --only: the model's sizes")
     parser.add_argument("--requests", type=int, default=64, help="with --only serve: requests of the workload")
     parser.add_argument("--workload", choices=["mixed", "shared-prefix"], default="mixed",
                         help="with --only serve: mixed prompt lengths, or long prompts that share a prefix in a pool too small for all")

@@ -1,0 +1,447 @@
+// Latent attention on tensor cores (mma.sync.m16n8k16, bfloat16 operands, float32 accumulation and softmax).
+//
+// The cache holds one row per token, `width` = rank + rot wide, shared by all heads; a query row
+// (token, head) is as wide; its score with a key row is their dot product times `scale`; the value of a
+// key row is its first `rank` elements.  Rows of a request's tokens are tiled 16 to a warp; all rows of
+// a tile read the same staged key rows (cp.async, double-buffered stages of KEYS rows), once for the
+// scores (ldmatrix) and once, transposed, as values.  A CTA accumulates DVC value columns; a latent
+// wider than that is divided among CTAs (blockIdx.y), each of which computes the scores again.
+//
+//  * whole rows (prefill and mixed batches): a CTA owns 64 rows (4 warps x 16) of one request and walks
+//    the keys up to its last row's position; a head's sink starts the running maximum and sum.
+//  * split keys (one token per request): a CTA owns the 16 heads of a request's token and one range of
+//    its keys; its 4 warps take a quarter of every stage each and are merged through shared memory;
+//    the ranges' partial sums go through float32 scratch to a merge kernel, which also adds the sink.
+#include "attention_bf16.cuh"
+
+using namespace sprout_attn;
+
+namespace {
+
+constexpr int THREADS = 128;
+constexpr int ROWS = 64;          // rows of a whole-rows CTA
+
+struct LatentParams {
+  const __nv_bfloat16* q;         // [tokens, heads * width]
+  const __nv_bfloat16* cache;     // [pages, 1, page_tokens, width]
+  const int* block_table; int table_stride;
+  const int* q_start;             // [requests + 1]
+  const int* positions;           // [tokens]
+  const int* context_lens;        // [requests] (split keys)
+  const float* sink;              // [heads] or null
+  __nv_bfloat16* out;             // [tokens, heads * rank]
+  float* part_o;                  // [requests, splits, heads, rank]   (split keys)
+  float* part_ml;                 // [requests, splits, heads, 2]
+  int requests, heads, width, rank, page_tokens, num_pages, split_keys, splits;
+  float scale;
+  int* status;
+};
+
+// One warp: scores of its 16 rows against NT * 8 staged keys, online softmax, O += P V over the CTA's columns.
+template <int DVC, int NT>
+__device__ __forceinline__ void attend_block(const __nv_bfloat16* sQ, const __nv_bfloat16* tK, int stride, int width,
+                                             int col0, int col_end, int key0, int limit0, int limit1, bool mask,
+                                             float scale_log2, float& m0, float& m1, float& l0, float& l1,
+                                             float (&o)[DVC / 8][4], int lane) {
+  const int qc = lane & 3;
+  float s[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+  const __nv_bfloat16* a_ptr = sQ + ((lane & 7) + ((lane >> 3) & 1) * 8) * stride + (lane >> 4) * 8;
+  const __nv_bfloat16* b_ptr = tK + ((lane & 7) + (lane >> 4) * 8) * stride + ((lane >> 3) & 1) * 8;
+#pragma unroll 2
+  for (int kk = 0; kk < width / 16; kk++) {
+    uint32_t a[4];
+    ldmatrix_x4(a, a_ptr + kk * 16);
+#pragma unroll
+    for (int n2 = 0; n2 < NT / 2; n2++) {
+      uint32_t b[4];
+      ldmatrix_x4(b, b_ptr + n2 * 16 * stride + kk * 16);
+      mma_bf16(s[2 * n2], a, b[0], b[1]);
+      mma_bf16(s[2 * n2 + 1], a, b[2], b[3]);
+    }
+  }
+  if (mask) {
+#pragma unroll
+    for (int i = 0; i < NT; i++) {
+      const int key = key0 + i * 8 + qc * 2;
+      if (key > limit0) s[i][0] = -INFINITY;
+      if (key + 1 > limit0) s[i][1] = -INFINITY;
+      if (key > limit1) s[i][2] = -INFINITY;
+      if (key + 1 > limit1) s[i][3] = -INFINITY;
+    }
+  }
+  float t0 = -INFINITY, t1 = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < NT; i++) {
+    t0 = fmaxf(t0, fmaxf(s[i][0], s[i][1]));
+    t1 = fmaxf(t1, fmaxf(s[i][2], s[i][3]));
+  }
+  t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 1));
+  t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 2));
+  t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 1));
+  t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 2));
+  const float n0 = fmaxf(m0, t0), n1 = fmaxf(m1, t1);          // running maxima of the unscaled scores
+  const float base0 = n0 == -INFINITY ? 0.f : n0 * scale_log2, base1 = n1 == -INFINITY ? 0.f : n1 * scale_log2;
+  const float alpha0 = m0 == -INFINITY ? 0.f : exp2f(m0 * scale_log2 - base0);
+  const float alpha1 = m1 == -INFINITY ? 0.f : exp2f(m1 * scale_log2 - base1);
+  m0 = n0; m1 = n1;
+  l0 *= alpha0; l1 *= alpha1;
+#pragma unroll
+  for (int i = 0; i < DVC / 8; i++) { o[i][0] *= alpha0; o[i][1] *= alpha0; o[i][2] *= alpha1; o[i][3] *= alpha1; }
+#pragma unroll
+  for (int i = 0; i < NT; i++) {
+    s[i][0] = exp2f(fmaf(s[i][0], scale_log2, -base0)); s[i][1] = exp2f(fmaf(s[i][1], scale_log2, -base0));
+    s[i][2] = exp2f(fmaf(s[i][2], scale_log2, -base1)); s[i][3] = exp2f(fmaf(s[i][3], scale_log2, -base1));
+    l0 += s[i][0] + s[i][1];
+    l1 += s[i][2] + s[i][3];
+  }
+  const __nv_bfloat16* v_ptr = tK + ((lane & 7) + ((lane >> 3) & 1) * 8) * stride + col0 + (lane >> 4) * 8;
+#pragma unroll
+  for (int kk = 0; kk < NT / 2; kk++) {
+    uint32_t a[4];
+    a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+    a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+    a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+    a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+    for (int d2 = 0; d2 < DVC / 16; d2++) {
+      if (col0 + d2 * 16 < col_end) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, v_ptr + kk * 16 * stride + d2 * 16);
+        mma_bf16(o[2 * d2], a, b[0], b[1]);
+        mma_bf16(o[2 * d2 + 1], a, b[2], b[3]);
+      }
+    }
+  }
+}
+
+// Offsets of a stage's key rows (by the first KEYS threads), then their copy into shared memory.
+template <int KEYS>
+__device__ __forceinline__ void find_rows(const LatentParams& p, const int* table, int first_key, int last_key,
+                                          long long* offsets, int tid) {
+  if (tid < KEYS) {
+    const int key = first_key + tid;
+    long long off = -1;
+    if (key <= last_key) {
+      const int page = table[key / p.page_tokens];
+      if (page < 0 || page >= p.num_pages) atomicOr(p.status, SPROUT_STATUS_BAD_PAGE);
+      else off = ((long long)page * p.page_tokens + key % p.page_tokens) * p.width;
+    }
+    offsets[tid] = off;
+  }
+}
+template <int KEYS>
+__device__ __forceinline__ void load_stage(const LatentParams& p, const long long* offsets, __nv_bfloat16* dst, int stride,
+                                           int tid) {
+  const int chunks = p.width / 8;
+  for (int idx = tid; idx < KEYS * chunks; idx += THREADS) {
+    const int row = idx / chunks, c = idx % chunks;
+    const long long off = offsets[row];
+    __nv_bfloat16* d = dst + row * stride + c * 8;
+    if (off >= 0) cp_async16(d, p.cache + off + c * 8);
+    else *(uint4*)d = make_uint4(0, 0, 0, 0);
+  }
+}
+
+// ------------------------------------------------------------------------------ whole rows
+template <int DVC, int KEYS>
+__global__ void __launch_bounds__(THREADS)
+latent_attention_rows_kernel(const LatentParams p) {
+  extern __shared__ __align__(16) uint8_t lsm[];
+  const int stride = p.width + 8;
+  __nv_bfloat16* sQ = (__nv_bfloat16*)lsm;            // [ROWS][stride]
+  __nv_bfloat16* sK = sQ + ROWS * stride;             // [2][KEYS][stride]
+  __shared__ int s_limit[ROWS];
+  __shared__ int s_token[ROWS];
+  __shared__ int s_head[ROWS];
+  __shared__ long long s_off[2][KEYS];
+
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int col0 = blockIdx.y * DVC, col_end = min(p.rank, col0 + DVC);
+
+  int r = 0, tile = blockIdx.x;
+  for (; r < p.requests; r++) {
+    const int tiles = ((p.q_start[r + 1] - p.q_start[r]) * p.heads + ROWS - 1) / ROWS;
+    if (tile < tiles) {
+      tile = (tile & 1) ? tiles - 1 - (tile >> 1) : (tile >> 1);      // long and short tiles alternate in launch order
+      break;
+    }
+    tile -= tiles;
+  }
+  if (r >= p.requests) return;
+  const int q0 = p.q_start[r], rows_total = (p.q_start[r + 1] - q0) * p.heads;
+  const int row_base = tile * ROWS;
+  const int* table = p.block_table + (size_t)r * p.table_stride;
+  if (tid < ROWS) {
+    const int gi = row_base + tid;
+    if (gi < rows_total) {
+      const int tok = q0 + gi / p.heads;
+      s_token[tid] = tok; s_head[tid] = gi % p.heads; s_limit[tid] = p.positions[tok];
+    } else {
+      s_token[tid] = -1; s_head[tid] = 0; s_limit[tid] = -1;
+    }
+  }
+  __syncthreads();
+  const int last_row = min(rows_total, row_base + ROWS) - 1 - row_base;
+  const int max_limit = s_limit[last_row];
+  const int stages = max_limit / KEYS + 1;
+  const int chunks = p.width / 8;
+  for (int idx = tid; idx < ROWS * chunks; idx += THREADS) {
+    const int row = idx / chunks, c = idx % chunks;
+    __nv_bfloat16* dst = sQ + row * stride + c * 8;
+    if (s_token[row] >= 0) cp_async16(dst, p.q + ((size_t)s_token[row] * p.heads + s_head[row]) * p.width + c * 8);
+    else *(uint4*)dst = make_uint4(0, 0, 0, 0);
+  }
+  find_rows<KEYS>(p, table, 0, max_limit, s_off[0], tid);
+  __syncthreads();
+  load_stage<KEYS>(p, s_off[0], sK, stride, tid);
+  cp_async_commit();
+
+  const int gr = lane >> 2, qc = lane & 3;
+  const int my_row0 = warp * 16 + gr, my_row1 = my_row0 + 8;
+  const int limit0 = s_limit[my_row0], limit1 = s_limit[my_row1];
+  const float scale_log2 = p.scale * 1.4426950408889634f;
+  // a sink starts the running maximum (in units of the unscaled score) and counts once in the sum
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  if (p.sink) {
+    m0 = p.sink[s_head[my_row0]] / p.scale; m1 = p.sink[s_head[my_row1]] / p.scale;
+    if (qc == 0) { l0 = 1.f; l1 = 1.f; }
+  }
+  float o[DVC / 8][4];
+#pragma unroll
+  for (int i = 0; i < DVC / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  const int warp_min_limit = s_limit[min(warp * 16, last_row)];
+  const int warp_limit = s_limit[min(warp * 16 + 15, last_row)];
+
+  for (int t = 0; t < stages; t++) {
+    const int buf = t & 1;
+    if (t + 1 < stages) find_rows<KEYS>(p, table, (t + 1) * KEYS, max_limit, s_off[buf ^ 1], tid);
+    __syncthreads();
+    if (t + 1 < stages) load_stage<KEYS>(p, s_off[buf ^ 1], sK + (buf ^ 1) * KEYS * stride, stride, tid);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const int key0 = t * KEYS;
+    if (warp * 16 <= last_row && key0 <= warp_limit)
+      attend_block<DVC, KEYS / 8>(sQ + warp * 16 * stride, sK + buf * KEYS * stride, stride, p.width, col0, col_end, key0,
+                                  limit0, limit1, key0 + KEYS - 1 > warp_min_limit, scale_log2, m0, m1, l0, l1, o, lane);
+  }
+  cp_async_wait<0>();
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+#pragma unroll
+  for (int half = 0; half < 2; half++) {
+    const int row = half ? my_row1 : my_row0;
+    if (s_token[row] < 0) continue;
+    __nv_bfloat16* dst = p.out + ((size_t)s_token[row] * p.heads + s_head[row]) * p.rank + col0 + qc * 2;
+    const float inv = 1.0f / (half ? l1 : l0);
+#pragma unroll
+    for (int i = 0; i < DVC / 8; i++)
+      if (col0 + i * 8 < col_end)
+        *(__nv_bfloat162*)(dst + i * 8) = __floats2bfloat162_rn(o[i][half * 2] * inv, o[i][half * 2 + 1] * inv);
+  }
+}
+
+// ------------------------------------------------------------------------------ split keys (one token per request)
+template <int DVC>
+__global__ void __launch_bounds__(THREADS)
+latent_attention_split_kernel(const LatentParams p) {
+  constexpr int KEYS = 64;
+  extern __shared__ __align__(16) uint8_t lsm[];
+  const int stride = p.width + 8;
+  __nv_bfloat16* sQ = (__nv_bfloat16*)lsm;            // [16][stride]
+  __nv_bfloat16* sK = sQ + 16 * stride;               // [2][KEYS][stride]; after the loop: the warps' partial sums
+  __shared__ long long s_off[2][KEYS];
+  __shared__ float s_ml[4][16][2];
+
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int groups = (p.heads + 15) / 16;
+  const int r = blockIdx.x / groups, head0 = (blockIdx.x % groups) * 16;
+  const int col0 = blockIdx.y * DVC, col_end = min(p.rank, col0 + DVC);
+  const int split = blockIdx.z;
+  const int limit = p.context_lens[r] - 1;            // the token's own position: the last key it sees
+  // the last range runs to the token's position, however the ranges were planned
+  const int first = split * p.split_keys, last = split == p.splits - 1 ? limit : min(limit, first + p.split_keys - 1);
+  const int stages = last >= first ? (last - first) / KEYS + 1 : 0;
+  const int* table = p.block_table + (size_t)r * p.table_stride;
+  const int chunks = p.width / 8;
+  const int token = p.q_start[r];
+  for (int idx = tid; idx < 16 * chunks; idx += THREADS) {
+    const int row = idx / chunks, c = idx % chunks;
+    __nv_bfloat16* dst = sQ + row * stride + c * 8;
+    if (head0 + row < p.heads) cp_async16(dst, p.q + ((size_t)token * p.heads + head0 + row) * p.width + c * 8);
+    else *(uint4*)dst = make_uint4(0, 0, 0, 0);
+  }
+  if (stages > 0) find_rows<KEYS>(p, table, first, last, s_off[0], tid);
+  __syncthreads();
+  if (stages > 0) load_stage<KEYS>(p, s_off[0], sK, stride, tid);
+  cp_async_commit();
+
+  const int gr = lane >> 2, qc = lane & 3;
+  const float scale_log2 = p.scale * 1.4426950408889634f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  float o[DVC / 8][4];
+#pragma unroll
+  for (int i = 0; i < DVC / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  for (int t = 0; t < stages; t++) {
+    const int buf = t & 1;
+    if (t + 1 < stages) find_rows<KEYS>(p, table, first + (t + 1) * KEYS, last, s_off[buf ^ 1], tid);
+    __syncthreads();
+    if (t + 1 < stages) load_stage<KEYS>(p, s_off[buf ^ 1], sK + (buf ^ 1) * KEYS * stride, stride, tid);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const int key0 = first + t * KEYS + warp * 16;    // this warp's quarter of the stage
+    if (key0 <= last)
+      attend_block<DVC, 2>(sQ, sK + (buf * KEYS + warp * 16) * stride, stride, p.width, col0, col_end, key0, last, last,
+                           key0 + 15 > last, scale_log2, m0, m1, l0, l1, o, lane);
+  }
+  cp_async_wait<0>();
+  __syncthreads();                                    // every warp is done with the stages: they become the exchange area
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  float* so = (float*)sK;                             // [4 warps][16 rows][DVC]
+  if (qc == 0) {
+    s_ml[warp][gr][0] = m0 == -INFINITY ? -INFINITY : m0 * p.scale; s_ml[warp][gr][1] = l0;
+    s_ml[warp][gr + 8][0] = m1 == -INFINITY ? -INFINITY : m1 * p.scale; s_ml[warp][gr + 8][1] = l1;
+  }
+#pragma unroll
+  for (int i = 0; i < DVC / 8; i++) {
+    *(float2*)(so + ((warp * 16 + gr) * DVC) + i * 8 + qc * 2) = make_float2(o[i][0], o[i][1]);
+    *(float2*)(so + ((warp * 16 + gr + 8) * DVC) + i * 8 + qc * 2) = make_float2(o[i][2], o[i][3]);
+  }
+  __syncthreads();
+  const int cols = col_end - col0;
+  for (int idx = tid; idx < 16 * cols; idx += THREADS) {
+    const int row = idx / cols, c = idx % cols;
+    if (head0 + row >= p.heads) continue;
+    float top = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; w++) top = fmaxf(top, s_ml[w][row][0]);
+    float sum = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+      const float f = s_ml[w][row][0] == -INFINITY ? 0.f : expf(s_ml[w][row][0] - top);
+      sum = fmaf(f, so[(w * 16 + row) * DVC + c], sum);
+      l = fmaf(f, s_ml[w][row][1], l);
+    }
+    const size_t at = ((size_t)r * p.splits + split) * p.heads + head0 + row;
+    p.part_o[at * p.rank + col0 + c] = sum;
+    if (c == 0 && blockIdx.y == 0) { p.part_ml[at * 2] = top; p.part_ml[at * 2 + 1] = l; }
+  }
+}
+
+// One block per (request, head): the ranges' partial sums and the sink become the output row.
+__global__ void __launch_bounds__(128)
+latent_attention_merge_kernel(const LatentParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x, h = blockIdx.y;
+  float top = p.sink ? p.sink[h] : -INFINITY;
+  for (int s = 0; s < p.splits; s++) top = fmaxf(top, p.part_ml[(((size_t)r * p.splits + s) * p.heads + h) * 2]);
+  float denom = p.sink ? expf(p.sink[h] - top) : 0.f;
+  for (int s = 0; s < p.splits; s++) {
+    const float* ml = p.part_ml + (((size_t)r * p.splits + s) * p.heads + h) * 2;
+    if (ml[0] != -INFINITY) denom = fmaf(expf(ml[0] - top), ml[1], denom);
+  }
+  const int token = p.q_start[r];
+  for (int c = threadIdx.x; c < p.rank; c += blockDim.x) {
+    float sum = 0.f;
+    for (int s = 0; s < p.splits; s++) {
+      const size_t at = ((size_t)r * p.splits + s) * p.heads + h;
+      const float m = p.part_ml[at * 2];
+      if (m != -INFINITY) sum = fmaf(expf(m - top), p.part_o[at * p.rank + c], sum);
+    }
+    p.out[((size_t)token * p.heads + h) * p.rank + c] = __float2bfloat16_rn(sum / denom);
+  }
+}
+
+template <typename K>
+int prepare(K kernel, size_t smem) {
+  static thread_local const void* done[16];
+  static thread_local int count = 0;
+  for (int i = 0; i < count; i++) if (done[i] == (const void*)kernel) return 0;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 4096) != cudaSuccess)
+    return sprout_fail("latent_attention: cannot raise the kernel's shared memory limit");
+  if (count < 16) done[count++] = (const void*)kernel;
+  (void)smem;
+  return 0;
+}
+
+constexpr size_t SMEM_LIMIT = 232448 - 4096;          // dynamic bytes a CTA may ask for beside the kernels' static arrays
+
+}  // namespace
+
+// Whether the tensor-core kernels take these sizes (else the caller runs the float32-arithmetic kernel).
+SPROUT_API int sprout_latent_attention_mma_supported(int width, int rank) {
+  if (width % 16 || rank % 16 || rank <= 0 || width < rank) return 0;
+  const size_t row_bytes = (size_t)(width + 8) * 2;
+  return (ROWS + 2 * 32) * row_bytes <= SMEM_LIMIT && (16 + 2 * 64) * row_bytes <= SMEM_LIMIT;
+}
+
+// Floats of scratch that split_keys mode needs: part_o then part_ml.
+SPROUT_API long long sprout_latent_attention_scratch_floats(int requests, int heads, int rank, int splits) {
+  return (long long)requests * splits * heads * (rank + 2);
+}
+
+// splits == 0: whole rows (any mix of portions and single tokens).  splits >= 1: every request brings one token
+// and its keys are divided into `splits` ranges of `split_keys` (a multiple of 64) keys.
+SPROUT_API int sprout_latent_attention_mma(const void* q, const void* cache, const int* block_table, int table_stride,
+                                           const int* q_start, const int* positions, const int* context_lens,
+                                           const float* sink, void* out, float* scratch, int tokens, int requests,
+                                           int heads, int width, int rank, int page_tokens, int num_pages, int splits,
+                                           int split_keys, float scale, int* status, cudaStream_t stream) {
+  SPROUT_REQUIRE(q && cache && block_table && q_start && positions && out && status, "latent_attention_mma: null pointer");
+  SPROUT_REQUIRE(tokens > 0 && requests > 0 && heads > 0 && page_tokens > 0 && num_pages > 0 && scale > 0.f,
+                 "latent_attention_mma: sizes and scale must be positive");
+  SPROUT_REQUIRE(sprout_latent_attention_mma_supported(width, rank),
+                 "latent_attention_mma: width (%d) and latent size (%d) must be multiples of 16 that fit shared memory", width, rank);
+  LatentParams p;
+  p.q = (const __nv_bfloat16*)q; p.cache = (const __nv_bfloat16*)cache; p.block_table = block_table; p.table_stride = table_stride;
+  p.q_start = q_start; p.positions = positions; p.context_lens = context_lens; p.sink = sink; p.out = (__nv_bfloat16*)out;
+  p.requests = requests; p.heads = heads; p.width = width; p.rank = rank; p.page_tokens = page_tokens; p.num_pages = num_pages;
+  p.split_keys = split_keys; p.splits = splits; p.scale = scale; p.status = status;
+  p.part_o = scratch; p.part_ml = scratch ? scratch + (size_t)requests * splits * heads * rank : nullptr;
+  const int chunks = (rank + 255) / 256;
+  const bool narrow = rank <= 128;
+  const size_t row_bytes = (size_t)(width + 8) * 2;
+  if (splits == 0) {
+    const long long tiles = ((long long)tokens * heads + ROWS - 1) / ROWS + requests;
+    SPROUT_REQUIRE(tiles <= 0x7fffffffLL, "latent_attention_mma: too many rows");
+    const bool keys64 = (ROWS + 2 * 64) * row_bytes <= SMEM_LIMIT;
+    const size_t smem = (ROWS + 2 * (keys64 ? 64 : 32)) * row_bytes;
+    dim3 grid((unsigned)tiles, narrow ? 1 : chunks);
+#define LAUNCH_ROWS(DVC, KEYS)                                                                           \
+    do {                                                                                                 \
+      if (prepare(latent_attention_rows_kernel<DVC, KEYS>, smem)) return 1;                              \
+      sprout_launch(latent_attention_rows_kernel<DVC, KEYS>, grid, dim3(THREADS), smem, stream, p);      \
+    } while (0)
+    if (narrow) { if (keys64) LAUNCH_ROWS(128, 64); else LAUNCH_ROWS(128, 32); }
+    else { if (keys64) LAUNCH_ROWS(256, 64); else LAUNCH_ROWS(256, 32); }
+#undef LAUNCH_ROWS
+    return sprout_check_launch("latent_attention_rows");
+  }
+  SPROUT_REQUIRE(tokens == requests && context_lens && scratch && split_keys > 0 && split_keys % 64 == 0,
+                 "latent_attention_mma: split keys need one token per request, context lengths, scratch and ranges of a multiple of 64 keys");
+  // the stages' room is used again for the warps' partial sums: [4][16][DVC] floats
+  const size_t exchange = (size_t)4 * 16 * (narrow ? 128 : 256) * sizeof(float);
+  const size_t smem = 16 * row_bytes + (2 * 64 * row_bytes > exchange ? 2 * 64 * row_bytes : exchange);
+  SPROUT_REQUIRE(smem <= SMEM_LIMIT, "latent_attention_mma: rows too wide for the split kernel's shared memory");
+  const int groups = (heads + 15) / 16;
+  dim3 grid(requests * groups, narrow ? 1 : chunks, splits);
+  if (narrow) {
+    if (prepare(latent_attention_split_kernel<128>, smem)) return 1;
+    sprout_launch(latent_attention_split_kernel<128>, grid, dim3(THREADS), smem, stream, p);
+  } else {
+    if (prepare(latent_attention_split_kernel<256>, smem)) return 1;
+    sprout_launch(latent_attention_split_kernel<256>, grid, dim3(THREADS), smem, stream, p);
+  }
+  if (int code = sprout_check_launch("latent_attention_split")) return code;
+  sprout_launch(latent_attention_merge_kernel, dim3(requests, heads), dim3(128), 0, stream, p);
+  return sprout_check_launch("latent_attention_merge");
+}

@@ -58,6 +58,8 @@ _SIGNATURES = {
     "sprout_latent_query_tail": [_P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_headwise_gemm": [_P, _L, _L, _P, _P, _L, _L, _I, _I, _I, _I, _I, _P],
     "sprout_latent_attention_simple": [_P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P],
+    "sprout_latent_attention_mma": [_P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P],
+    "sprout_latent_attention_mma_supported": [_I, _I],
     "sprout_depth_average": [_P, _P, _P, _I, _L, _P],
     "sprout_softcap": [_P, _F, _L, _P],
 }
@@ -971,10 +973,69 @@ def latent_attention_simple(qlat, cache, block_table, seq_of_token, positions, s
          cache.shape[2], cache.shape[0], float(scale), _ptr(status, "status", torch.int32), _stream())
 
 
+def latent_attention_mma_supported(width: int, rank: int) -> bool:
+    """Whether the tensor-core latent attention kernels take rows of ``width`` with a latent of ``rank``
+    (multiples of 16 whose stages fit shared memory)."""
+    lib = _lib or load_library()
+    return bool(lib.sprout_latent_attention_mma_supported(int(width), int(rank)))
+
+
+def latent_split_plan(requests: int, heads: int, rank: int, planned_keys: int) -> tuple[int, int]:
+    """(ranges, keys per range) for a step of one token per request: enough CTAs for two per SM, ranges of
+    a multiple of 64 keys, at most 64 of them.  It follows the contexts' length alone, so a captured
+    step is replayed for steps that plan alike."""
+    groups, chunks = -(-heads // 16), 1 if rank <= 128 else -(-rank // 256)
+    stages = max(1, -(-planned_keys // 64))
+    splits = max(1, min(2 * sm_count() // max(1, requests * groups * chunks), stages, 64))
+    split_keys = -(-stages // splits) * 64
+    return -(-stages * 64 // split_keys), split_keys
+
+
+def latent_attention_mma(qlat, cache, block_table, q_start, positions, context_lens, sink, out, heads: int, rank: int,
+                         scale: float, status, requests: int, splits: int = 0, split_keys: int = 0):
+    """The tensor-core form of ``latent_attention_simple`` (bfloat16).  ``splits`` 0: rows of any mix of
+    portions and single tokens, 64 to a CTA.  ``splits`` >= 1: one token per request, its keys divided into
+    ranges of ``split_keys`` that are merged through float32 scratch."""
+    T = qlat.shape[0]
+    width = cache.shape[3]
+    if cache.dim() != 4 or cache.shape[1] != 1 or not cache.is_contiguous() or cache.dtype != torch.bfloat16 \
+            or qlat.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or not qlat.is_contiguous() or not out.is_contiguous() \
+            or tuple(qlat.shape) != (T, heads * width) or tuple(out.shape) != (T, heads * rank) \
+            or (sink is not None and sink.numel() != heads) or q_start.numel() != requests + 1 or positions.numel() != T:
+        raise KernelError("latent_attention_mma: shapes or dtypes do not fit")
+    _rows_contiguous(block_table, "block_table")
+    scratch = None
+    if splits:
+        if T != requests or context_lens is None or context_lens.numel() != requests:
+            raise KernelError("latent_attention_mma: split keys need one token and one context length per request")
+        scratch = torch.empty(requests * splits * heads * (rank + 2), dtype=torch.float32, device=qlat.device)
+    _run("sprout_latent_attention_mma", _ptr(qlat, "qlat"), _ptr(cache, "cache"), _ptr(block_table, "block_table", torch.int32),
+         block_table.stride(0), _ptr(q_start, "q_start", torch.int32), _ptr(positions, "positions", torch.int32),
+         _ptr(context_lens, "context_lens", torch.int32, True), _ptr(sink, "sink", torch.float32, True), _ptr(out, "out"),
+         _ptr(scratch, "scratch", torch.float32, True), T, requests, heads, width, rank, cache.shape[2], cache.shape[0],
+         int(splits), int(split_keys), float(scale), _ptr(status, "status", torch.int32), _stream())
+    if splits:
+        global LAUNCHES
+        LAUNCHES += 1                       # the merge kernel
+
+
+LATENT_ATTENTION = os.environ.get("SPROUT_LATENT_ATTENTION", "auto")      # "simple": the float32-arithmetic kernel for every step
+
+
 def latent_attention(qlat, cache, ctx, sink, out, heads: int, rank: int, scale: float, status):
     """Latent attention of the step's rows over their requests' pages (``cache`` is a CacheView whose
-    key buffer holds the rows): picks the kernel for the dtype and the step's shape."""
-    latent_attention_simple(qlat, cache.k, cache.block_table, ctx.seq_of_token, ctx.positions, sink, out, heads, rank, scale, status)
+    key buffer holds the rows).  float32 runs the plain kernel (the true 32-bit path), and so do sizes the
+    tensor-core kernels do not take; bfloat16 runs the split-key kernel when every request brings one
+    token and the whole-rows kernel otherwise."""
+    width = cache.k.shape[3]
+    if qlat.dtype != torch.bfloat16 or LATENT_ATTENTION == "simple" or not latent_attention_mma_supported(width, rank):
+        return latent_attention_simple(qlat, cache.k, cache.block_table, ctx.seq_of_token, ctx.positions, sink, out, heads, rank,
+                                       scale, status)
+    splits = split_keys = 0
+    if ctx.max_q_len == 1:
+        splits, split_keys = latent_split_plan(ctx.num_seqs, heads, rank, ctx.planned_context or ctx.max_context)
+    latent_attention_mma(qlat, cache.k, cache.block_table, ctx.q_start, ctx.positions, ctx.context_lens, sink, out, heads, rank,
+                         scale, status, ctx.num_seqs, splits, split_keys)
 
 
 def depth_average(history, x, weights, n: int):

@@ -53,6 +53,10 @@ class LatentAttention(Part):
     def state_spec(self):
         return None
 
+    def decode_plan(self, requests: int, max_keys: int, planned_context: int, page_tokens: int):
+        """How a step of one token per request divides its keys among CTAs: it follows the contexts' length."""
+        return kernels.latent_split_plan(requests, self.heads, self.kv_rank, planned_context)
+
     # ---- weights
     def tensor_decls(self):
         n, q_width = self.names, self.heads * (self.dim + self.rot_dim)
