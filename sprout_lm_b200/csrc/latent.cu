@@ -18,7 +18,9 @@
 //  * depth_average:     keeps a layer's result in a history and replaces the stream by a weighted
 //                       sum of the history so far.
 //  * softcap:           x = cap * tanh(x / cap), in place.
-#include "common.cuh"
+#include "attention_bf16.cuh"
+
+using namespace sprout_attn;
 
 namespace {
 
@@ -226,6 +228,74 @@ headwise_gemm_kernel(const T* __restrict__ A, long long a_row, long long a_head,
   }
 }
 
+// The same on tensor cores (bfloat16): a CTA makes 64 rows x 64 columns of one head, 4 warps of 16 rows each,
+// K in steps of 32 through shared memory (ldmatrix, mma.sync.m16n8k16, float32 accumulation).
+constexpr int TB = 64, TK = 32, TSTRIDE = TK + 8;
+
+__global__ void __launch_bounds__(128)
+headwise_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, long long a_row, long long a_head,
+                         const __nv_bfloat16* __restrict__ W, __nv_bfloat16* __restrict__ out, long long o_row,
+                         long long o_head, int M, int N, int K) {
+  __shared__ __align__(16) __nv_bfloat16 As[2][TB][TSTRIDE];
+  __shared__ __align__(16) __nv_bfloat16 Ws[2][TB][TSTRIDE];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int head = blockIdx.z, m0 = blockIdx.y * TB, n0 = blockIdx.x * TB;
+  const __nv_bfloat16* a = A + head * a_head;
+  const __nv_bfloat16* w = W + (size_t)head * N * K;
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  auto load = [&](int buf, int k0) {
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+      const int idx = tid + i * 128, row = idx >> 2, c = (idx & 3) * 8;
+      const bool in_k = k0 + c < K;
+      if (m0 + row < M && in_k) cp_async16(&As[buf][row][c], a + (size_t)(m0 + row) * a_row + k0 + c);
+      else *(uint4*)&As[buf][row][c] = make_uint4(0, 0, 0, 0);
+      if (n0 + row < N && in_k) cp_async16(&Ws[buf][row][c], w + (size_t)(n0 + row) * K + k0 + c);
+      else *(uint4*)&Ws[buf][row][c] = make_uint4(0, 0, 0, 0);
+    }
+  };
+  const int steps = (K + TK - 1) / TK;
+  load(0, 0);
+  cp_async_commit();
+  for (int t = 0; t < steps; t++) {
+    const int buf = t & 1;
+    if (t + 1 < steps) load(buf ^ 1, (t + 1) * TK);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < TK / 16; kk++) {
+      uint32_t af[4];
+      ldmatrix_x4(af, &As[buf][warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][kk * 16 + (lane >> 4) * 8]);
+#pragma unroll
+      for (int n2 = 0; n2 < 4; n2++) {
+        uint32_t b[4];
+        ldmatrix_x4(b, &Ws[buf][n2 * 16 + (lane & 7) + (lane >> 4) * 8][kk * 16 + ((lane >> 3) & 1) * 8]);
+        mma_bf16(acc[2 * n2], af, b[0], b[1]);
+        mma_bf16(acc[2 * n2 + 1], af, b[2], b[3]);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  const int gr = lane >> 2, qc = lane & 3;
+#pragma unroll
+  for (int half = 0; half < 2; half++) {
+    const int gm = m0 + warp * 16 + gr + half * 8;
+    if (gm >= M) continue;
+    __nv_bfloat16* dst = out + (size_t)gm * o_row + head * o_head;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const int gn = n0 + i * 8 + qc * 2;
+      if (gn < N) *(__nv_bfloat162*)(dst + gn) = __floats2bfloat162_rn(acc[i][half * 2], acc[i][half * 2 + 1]);
+    }
+  }
+}
+
 // ---------------------------------------------------------------- latent_attention_simple
 // One block per (token, head).  Keys are walked in chunks of 128 aligned to absolute position with a
 // running maximum and sum that start from the head's sink (maximum = sink, sum = 1) when one is given.
@@ -424,6 +494,11 @@ SPROUT_API int sprout_headwise_gemm(const void* a, long long a_row, long long a_
   if (dtype == SPROUT_F32)
     sprout_launch(headwise_gemm_kernel<float>, grid, dim3(HTHREADS), 0, stream, (const float*)a, a_row, a_head, (const float*)w,
                   (float*)out, o_row, o_head, rows, n, k);
+  else if (dtype == SPROUT_BF16 && k % 8 == 0 && a_row % 8 == 0 && a_head % 8 == 0 && n % 2 == 0 && o_row % 2 == 0 && o_head % 2 == 0 &&
+           ((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)out & 3) == 0)
+    // rows that start on 16-byte boundaries and pairs of outputs on 4-byte ones: the tensor-core kernel
+    sprout_launch(headwise_gemm_mma_kernel, grid, dim3(128), 0, stream, (const __nv_bfloat16*)a, a_row, a_head,
+                  (const __nv_bfloat16*)w, (__nv_bfloat16*)out, o_row, o_head, rows, n, k);
   else if (dtype == SPROUT_BF16)
     sprout_launch(headwise_gemm_kernel<__nv_bfloat16>, grid, dim3(HTHREADS), 0, stream, (const __nv_bfloat16*)a, a_row, a_head,
                   (const __nv_bfloat16*)w, (__nv_bfloat16*)out, o_row, o_head, rows, n, k);

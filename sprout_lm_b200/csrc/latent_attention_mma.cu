@@ -5,21 +5,23 @@
 // key row is its first `rank` elements.  Rows of a request's tokens are tiled 16 to a warp; all rows of
 // a tile read the same staged key rows (cp.async, double-buffered stages of KEYS rows), once for the
 // scores (ldmatrix) and once, transposed, as values.  A CTA accumulates DVC value columns; a latent
-// wider than that is divided among CTAs (blockIdx.y), each of which computes the scores again.
+// wider than a CTA's blocks is divided among CTAs (blockIdx.y), each of which computes the scores again.
 //
-//  * whole rows (prefill and mixed batches): a CTA owns 64 rows (4 warps x 16) of one request and walks
-//    the keys up to its last row's position; a head's sink starts the running maximum and sum.
+//  * whole rows (prefill and mixed batches): a CTA of 8 warps owns 128 rows of one request, or 64 rows
+//    with each half of the warps taking one of two blocks of DVC value columns (both halves compute the
+//    scores; the staged keys and the query rows are shared), and walks the keys up to its last row's
+//    position; a head's sink starts the running maximum and sum.
 //  * split keys (one token per request): a CTA owns the 16 heads of a request's token and one range of
-//    its keys; its 4 warps take a quarter of every stage each and are merged through shared memory;
-//    the ranges' partial sums go through float32 scratch to a merge kernel, which also adds the sink.
+//    its keys; 4 warps per block of value columns take a quarter of every stage each and are merged
+//    through shared memory; the ranges' partial sums go through float32 scratch to a merge kernel,
+//    which also adds the sink.
 #include "attention_bf16.cuh"
 
 using namespace sprout_attn;
 
 namespace {
 
-constexpr int THREADS = 128;
-constexpr int ROWS = 64;          // rows of a whole-rows CTA
+constexpr int WARPS = 8;          // of a whole-rows CTA
 
 struct LatentParams {
   const __nv_bfloat16* q;         // [tokens, heads * width]
@@ -49,16 +51,44 @@ __device__ __forceinline__ void attend_block(const __nv_bfloat16* sQ, const __nv
   for (int i = 0; i < NT; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
   const __nv_bfloat16* a_ptr = sQ + ((lane & 7) + ((lane >> 3) & 1) * 8) * stride + (lane >> 4) * 8;
   const __nv_bfloat16* b_ptr = tK + ((lane & 7) + (lane >> 4) * 8) * stride + ((lane >> 3) & 1) * 8;
+  if (NT == 2) {
+    // one pair of tiles: even and odd k-steps go to accumulators of their own (two chains instead of one)
+    float s2[2][4];
+    s2[0][0] = s2[0][1] = s2[0][2] = s2[0][3] = s2[1][0] = s2[1][1] = s2[1][2] = s2[1][3] = 0.f;
+    const int steps = width / 16;
 #pragma unroll 2
-  for (int kk = 0; kk < width / 16; kk++) {
-    uint32_t a[4];
-    ldmatrix_x4(a, a_ptr + kk * 16);
+    for (int kk = 0; kk + 1 < steps; kk += 2) {
+      uint32_t a[4], b[4], a2[4], b2[4];
+      ldmatrix_x4(a, a_ptr + kk * 16);
+      ldmatrix_x4(b, b_ptr + kk * 16);
+      ldmatrix_x4(a2, a_ptr + kk * 16 + 16);
+      ldmatrix_x4(b2, b_ptr + kk * 16 + 16);
+      mma_bf16(s[0], a, b[0], b[1]);
+      mma_bf16(s[1], a, b[2], b[3]);
+      mma_bf16(s2[0], a2, b2[0], b2[1]);
+      mma_bf16(s2[1], a2, b2[2], b2[3]);
+    }
+    if (steps & 1) {
+      uint32_t a[4], b[4];
+      ldmatrix_x4(a, a_ptr + (steps - 1) * 16);
+      ldmatrix_x4(b, b_ptr + (steps - 1) * 16);
+      mma_bf16(s[0], a, b[0], b[1]);
+      mma_bf16(s[1], a, b[2], b[3]);
+    }
 #pragma unroll
-    for (int n2 = 0; n2 < NT / 2; n2++) {
-      uint32_t b[4];
-      ldmatrix_x4(b, b_ptr + n2 * 16 * stride + kk * 16);
-      mma_bf16(s[2 * n2], a, b[0], b[1]);
-      mma_bf16(s[2 * n2 + 1], a, b[2], b[3]);
+    for (int j = 0; j < 4; j++) { s[0][j] += s2[0][j]; s[1][j] += s2[1][j]; }
+  } else {
+#pragma unroll 2
+    for (int kk = 0; kk < width / 16; kk++) {
+      uint32_t a[4];
+      ldmatrix_x4(a, a_ptr + kk * 16);
+#pragma unroll
+      for (int n2 = 0; n2 < NT / 2; n2++) {
+        uint32_t b[4];
+        ldmatrix_x4(b, b_ptr + n2 * 16 * stride + kk * 16);
+        mma_bf16(s[2 * n2], a, b[0], b[1]);
+        mma_bf16(s[2 * n2 + 1], a, b[2], b[3]);
+      }
     }
   }
   if (mask) {
@@ -131,23 +161,33 @@ __device__ __forceinline__ void find_rows(const LatentParams& p, const int* tabl
     offsets[tid] = off;
   }
 }
+// rows [0, rows) of 16-byte pieces: thread tid takes pieces tid, tid + threads, ... (row and piece advance without a division)
+template <typename F>
+__device__ __forceinline__ void for_pieces(int rows, int pieces, int tid, int threads, F f) {
+  int row = tid / pieces, c = tid % pieces;
+  const int drow = threads / pieces, dc = threads % pieces;
+  while (row < rows) {
+    f(row, c);
+    row += drow; c += dc;
+    if (c >= pieces) { c -= pieces; row++; }
+  }
+}
 template <int KEYS>
 __device__ __forceinline__ void load_stage(const LatentParams& p, const long long* offsets, __nv_bfloat16* dst, int stride,
-                                           int tid) {
-  const int chunks = p.width / 8;
-  for (int idx = tid; idx < KEYS * chunks; idx += THREADS) {
-    const int row = idx / chunks, c = idx % chunks;
+                                           int tid, int threads) {
+  for_pieces(KEYS, p.width / 8, tid, threads, [&](int row, int c) {
     const long long off = offsets[row];
     __nv_bfloat16* d = dst + row * stride + c * 8;
     if (off >= 0) cp_async16(d, p.cache + off + c * 8);
     else *(uint4*)d = make_uint4(0, 0, 0, 0);
-  }
+  });
 }
 
 // ------------------------------------------------------------------------------ whole rows
-template <int DVC, int KEYS>
-__global__ void __launch_bounds__(THREADS)
+template <int DVC, int KEYS, int CHUNKS>
+__global__ void __launch_bounds__(WARPS * 32)
 latent_attention_rows_kernel(const LatentParams p) {
+  constexpr int THREADS = WARPS * 32, GROUPS = WARPS / CHUNKS, ROWS = GROUPS * 16;
   extern __shared__ __align__(16) uint8_t lsm[];
   const int stride = p.width + 8;
   __nv_bfloat16* sQ = (__nv_bfloat16*)lsm;            // [ROWS][stride]
@@ -160,7 +200,8 @@ latent_attention_rows_kernel(const LatentParams p) {
   pdl_launch_dependents();
   pdl_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int col0 = blockIdx.y * DVC, col_end = min(p.rank, col0 + DVC);
+  const int group = warp % GROUPS;                    // which 16 rows
+  const int col0 = (blockIdx.y * CHUNKS + warp / GROUPS) * DVC, col_end = min(p.rank, col0 + DVC);
 
   int r = 0, tile = blockIdx.x;
   for (; r < p.requests; r++) {
@@ -188,20 +229,18 @@ latent_attention_rows_kernel(const LatentParams p) {
   const int last_row = min(rows_total, row_base + ROWS) - 1 - row_base;
   const int max_limit = s_limit[last_row];
   const int stages = max_limit / KEYS + 1;
-  const int chunks = p.width / 8;
-  for (int idx = tid; idx < ROWS * chunks; idx += THREADS) {
-    const int row = idx / chunks, c = idx % chunks;
+  for_pieces(ROWS, p.width / 8, tid, THREADS, [&](int row, int c) {
     __nv_bfloat16* dst = sQ + row * stride + c * 8;
     if (s_token[row] >= 0) cp_async16(dst, p.q + ((size_t)s_token[row] * p.heads + s_head[row]) * p.width + c * 8);
     else *(uint4*)dst = make_uint4(0, 0, 0, 0);
-  }
+  });
   find_rows<KEYS>(p, table, 0, max_limit, s_off[0], tid);
   __syncthreads();
-  load_stage<KEYS>(p, s_off[0], sK, stride, tid);
+  load_stage<KEYS>(p, s_off[0], sK, stride, tid, THREADS);
   cp_async_commit();
 
   const int gr = lane >> 2, qc = lane & 3;
-  const int my_row0 = warp * 16 + gr, my_row1 = my_row0 + 8;
+  const int my_row0 = group * 16 + gr, my_row1 = my_row0 + 8;
   const int limit0 = s_limit[my_row0], limit1 = s_limit[my_row1];
   const float scale_log2 = p.scale * 1.4426950408889634f;
   // a sink starts the running maximum (in units of the unscaled score) and counts once in the sum
@@ -213,25 +252,27 @@ latent_attention_rows_kernel(const LatentParams p) {
   float o[DVC / 8][4];
 #pragma unroll
   for (int i = 0; i < DVC / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-  const int warp_min_limit = s_limit[min(warp * 16, last_row)];
-  const int warp_limit = s_limit[min(warp * 16 + 15, last_row)];
+  const int warp_min_limit = s_limit[min(group * 16, last_row)];
+  const int warp_limit = s_limit[min(group * 16 + 15, last_row)];
+  const bool active = group * 16 <= last_row && col0 < p.rank;
 
   for (int t = 0; t < stages; t++) {
     const int buf = t & 1;
     if (t + 1 < stages) find_rows<KEYS>(p, table, (t + 1) * KEYS, max_limit, s_off[buf ^ 1], tid);
     __syncthreads();
-    if (t + 1 < stages) load_stage<KEYS>(p, s_off[buf ^ 1], sK + (buf ^ 1) * KEYS * stride, stride, tid);
+    if (t + 1 < stages) load_stage<KEYS>(p, s_off[buf ^ 1], sK + (buf ^ 1) * KEYS * stride, stride, tid, THREADS);
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
     const int key0 = t * KEYS;
-    if (warp * 16 <= last_row && key0 <= warp_limit)
-      attend_block<DVC, KEYS / 8>(sQ + warp * 16 * stride, sK + buf * KEYS * stride, stride, p.width, col0, col_end, key0,
+    if (active && key0 <= warp_limit)
+      attend_block<DVC, KEYS / 8>(sQ + group * 16 * stride, sK + buf * KEYS * stride, stride, p.width, col0, col_end, key0,
                                   limit0, limit1, key0 + KEYS - 1 > warp_min_limit, scale_log2, m0, m1, l0, l1, o, lane);
   }
   cp_async_wait<0>();
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  if (!active) return;
 #pragma unroll
   for (int half = 0; half < 2; half++) {
     const int row = half ? my_row1 : my_row0;
@@ -246,10 +287,10 @@ latent_attention_rows_kernel(const LatentParams p) {
 }
 
 // ------------------------------------------------------------------------------ split keys (one token per request)
-template <int DVC>
-__global__ void __launch_bounds__(THREADS)
+template <int DVC, int CHUNKS>
+__global__ void __launch_bounds__(CHUNKS * 128)
 latent_attention_split_kernel(const LatentParams p) {
-  constexpr int KEYS = 64;
+  constexpr int KEYS = 64, THREADS = CHUNKS * 128;
   extern __shared__ __align__(16) uint8_t lsm[];
   const int stride = p.width + 8;
   __nv_bfloat16* sQ = (__nv_bfloat16*)lsm;            // [16][stride]
@@ -260,26 +301,26 @@ latent_attention_split_kernel(const LatentParams p) {
   pdl_launch_dependents();
   pdl_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int quarter = warp & 3, chunk = warp >> 2;    // which 16 keys of a stage, which block of value columns
   const int groups = (p.heads + 15) / 16;
   const int r = blockIdx.x / groups, head0 = (blockIdx.x % groups) * 16;
-  const int col0 = blockIdx.y * DVC, col_end = min(p.rank, col0 + DVC);
+  const int cta_col0 = blockIdx.y * CHUNKS * DVC, cta_col_end = min(p.rank, cta_col0 + CHUNKS * DVC);
+  const int col0 = cta_col0 + chunk * DVC, col_end = min(p.rank, col0 + DVC);
   const int split = blockIdx.z;
   const int limit = p.context_lens[r] - 1;            // the token's own position: the last key it sees
   // the last range runs to the token's position, however the ranges were planned
   const int first = split * p.split_keys, last = split == p.splits - 1 ? limit : min(limit, first + p.split_keys - 1);
   const int stages = last >= first ? (last - first) / KEYS + 1 : 0;
   const int* table = p.block_table + (size_t)r * p.table_stride;
-  const int chunks = p.width / 8;
   const int token = p.q_start[r];
-  for (int idx = tid; idx < 16 * chunks; idx += THREADS) {
-    const int row = idx / chunks, c = idx % chunks;
+  for_pieces(16, p.width / 8, tid, THREADS, [&](int row, int c) {
     __nv_bfloat16* dst = sQ + row * stride + c * 8;
     if (head0 + row < p.heads) cp_async16(dst, p.q + ((size_t)token * p.heads + head0 + row) * p.width + c * 8);
     else *(uint4*)dst = make_uint4(0, 0, 0, 0);
-  }
+  });
   if (stages > 0) find_rows<KEYS>(p, table, first, last, s_off[0], tid);
   __syncthreads();
-  if (stages > 0) load_stage<KEYS>(p, s_off[0], sK, stride, tid);
+  if (stages > 0) load_stage<KEYS>(p, s_off[0], sK, stride, tid, THREADS);
   cp_async_commit();
 
   const int gr = lane >> 2, qc = lane & 3;
@@ -292,23 +333,23 @@ latent_attention_split_kernel(const LatentParams p) {
     const int buf = t & 1;
     if (t + 1 < stages) find_rows<KEYS>(p, table, first + (t + 1) * KEYS, last, s_off[buf ^ 1], tid);
     __syncthreads();
-    if (t + 1 < stages) load_stage<KEYS>(p, s_off[buf ^ 1], sK + (buf ^ 1) * KEYS * stride, stride, tid);
+    if (t + 1 < stages) load_stage<KEYS>(p, s_off[buf ^ 1], sK + (buf ^ 1) * KEYS * stride, stride, tid, THREADS);
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
-    const int key0 = first + t * KEYS + warp * 16;    // this warp's quarter of the stage
-    if (key0 <= last)
-      attend_block<DVC, 2>(sQ, sK + (buf * KEYS + warp * 16) * stride, stride, p.width, col0, col_end, key0, last, last,
+    const int key0 = first + t * KEYS + quarter * 16; // this warp's quarter of the stage
+    if (key0 <= last && col0 < p.rank)
+      attend_block<DVC, 2>(sQ, sK + (buf * KEYS + quarter * 16) * stride, stride, p.width, col0, col_end, key0, last, last,
                            key0 + 15 > last, scale_log2, m0, m1, l0, l1, o, lane);
   }
   cp_async_wait<0>();
   __syncthreads();                                    // every warp is done with the stages: they become the exchange area
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-  float* so = (float*)sK;                             // [4 warps][16 rows][DVC]
-  if (qc == 0) {
-    s_ml[warp][gr][0] = m0 == -INFINITY ? -INFINITY : m0 * p.scale; s_ml[warp][gr][1] = l0;
-    s_ml[warp][gr + 8][0] = m1 == -INFINITY ? -INFINITY : m1 * p.scale; s_ml[warp][gr + 8][1] = l1;
+  float* so = (float*)sK;                             // [CHUNKS][4 quarters][16 rows][DVC]
+  if (qc == 0 && chunk == 0) {                        // every block of columns saw the same scores
+    s_ml[quarter][gr][0] = m0 == -INFINITY ? -INFINITY : m0 * p.scale; s_ml[quarter][gr][1] = l0;
+    s_ml[quarter][gr + 8][0] = m1 == -INFINITY ? -INFINITY : m1 * p.scale; s_ml[quarter][gr + 8][1] = l1;
   }
 #pragma unroll
   for (int i = 0; i < DVC / 8; i++) {
@@ -316,7 +357,7 @@ latent_attention_split_kernel(const LatentParams p) {
     *(float2*)(so + ((warp * 16 + gr + 8) * DVC) + i * 8 + qc * 2) = make_float2(o[i][2], o[i][3]);
   }
   __syncthreads();
-  const int cols = col_end - col0;
+  const int cols = cta_col_end - cta_col0;
   for (int idx = tid; idx < 16 * cols; idx += THREADS) {
     const int row = idx / cols, c = idx % cols;
     if (head0 + row >= p.heads) continue;
@@ -327,11 +368,11 @@ latent_attention_split_kernel(const LatentParams p) {
 #pragma unroll
     for (int w = 0; w < 4; w++) {
       const float f = s_ml[w][row][0] == -INFINITY ? 0.f : expf(s_ml[w][row][0] - top);
-      sum = fmaf(f, so[(w * 16 + row) * DVC + c], sum);
+      sum = fmaf(f, so[(((c / DVC) * 4 + w) * 16 + row) * DVC + c % DVC], sum);
       l = fmaf(f, s_ml[w][row][1], l);
     }
     const size_t at = ((size_t)r * p.splits + split) * p.heads + head0 + row;
-    p.part_o[at * p.rank + col0 + c] = sum;
+    p.part_o[at * p.rank + cta_col0 + c] = sum;
     if (c == 0 && blockIdx.y == 0) { p.part_ml[at * 2] = top; p.part_ml[at * 2 + 1] = l; }
   }
 }
@@ -361,19 +402,26 @@ latent_attention_merge_kernel(const LatentParams p) {
   }
 }
 
+constexpr size_t SMEM_LIMIT = 232448 - 4096;          // dynamic bytes a CTA may ask for beside the kernels' static arrays
+
 template <typename K>
-int prepare(K kernel, size_t smem) {
-  static thread_local const void* done[16];
+int prepare(K kernel) {
+  static thread_local const void* done[32];
   static thread_local int count = 0;
   for (int i = 0; i < count; i++) if (done[i] == (const void*)kernel) return 0;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 4096) != cudaSuccess)
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT) != cudaSuccess)
     return sprout_fail("latent_attention: cannot raise the kernel's shared memory limit");
-  if (count < 16) done[count++] = (const void*)kernel;
-  (void)smem;
+  if (count < 32) done[count++] = (const void*)kernel;
   return 0;
 }
 
-constexpr size_t SMEM_LIMIT = 232448 - 4096;          // dynamic bytes a CTA may ask for beside the kernels' static arrays
+// How a latent of `rank` columns is divided: DVC columns per warp, `chunks` such blocks per CTA, CTAs along y.
+struct Division { int dvc, chunks, ctas; };
+inline Division divide(int rank) {
+  if (rank <= 128) return {128, 1, 1};
+  if (rank <= 256) return {256, 1, 1};
+  return {256, 2, (rank + 511) / 512};
+}
 
 }  // namespace
 
@@ -381,16 +429,13 @@ constexpr size_t SMEM_LIMIT = 232448 - 4096;          // dynamic bytes a CTA may
 SPROUT_API int sprout_latent_attention_mma_supported(int width, int rank) {
   if (width % 16 || rank % 16 || rank <= 0 || width < rank) return 0;
   const size_t row_bytes = (size_t)(width + 8) * 2;
-  return (ROWS + 2 * 32) * row_bytes <= SMEM_LIMIT && (16 + 2 * 64) * row_bytes <= SMEM_LIMIT;
-}
-
-// Floats of scratch that split_keys mode needs: part_o then part_ml.
-SPROUT_API long long sprout_latent_attention_scratch_floats(int requests, int heads, int rank, int splits) {
-  return (long long)requests * splits * heads * (rank + 2);
+  const int rows = 16 * WARPS / divide(rank).chunks;
+  return (rows + 2 * 32) * row_bytes <= SMEM_LIMIT && (16 + 2 * 64) * row_bytes <= SMEM_LIMIT;
 }
 
 // splits == 0: whole rows (any mix of portions and single tokens).  splits >= 1: every request brings one token
-// and its keys are divided into `splits` ranges of `split_keys` (a multiple of 64) keys.
+// and its keys are divided into `splits` ranges of `split_keys` (a multiple of 64) keys; `scratch` then holds
+// requests * splits * heads * (rank + 2) floats.
 SPROUT_API int sprout_latent_attention_mma(const void* q, const void* cache, const int* block_table, int table_stride,
                                            const int* q_start, const int* positions, const int* context_lens,
                                            const float* sink, void* out, float* scratch, int tokens, int requests,
@@ -407,40 +452,42 @@ SPROUT_API int sprout_latent_attention_mma(const void* q, const void* cache, con
   p.requests = requests; p.heads = heads; p.width = width; p.rank = rank; p.page_tokens = page_tokens; p.num_pages = num_pages;
   p.split_keys = split_keys; p.splits = splits; p.scale = scale; p.status = status;
   p.part_o = scratch; p.part_ml = scratch ? scratch + (size_t)requests * splits * heads * rank : nullptr;
-  const int chunks = (rank + 255) / 256;
-  const bool narrow = rank <= 128;
+  const Division d = divide(rank);
   const size_t row_bytes = (size_t)(width + 8) * 2;
   if (splits == 0) {
-    const long long tiles = ((long long)tokens * heads + ROWS - 1) / ROWS + requests;
+    const int rows = 16 * WARPS / d.chunks;
+    const long long tiles = ((long long)tokens * heads + rows - 1) / rows + requests;
     SPROUT_REQUIRE(tiles <= 0x7fffffffLL, "latent_attention_mma: too many rows");
-    const bool keys64 = (ROWS + 2 * 64) * row_bytes <= SMEM_LIMIT;
-    const size_t smem = (ROWS + 2 * (keys64 ? 64 : 32)) * row_bytes;
-    dim3 grid((unsigned)tiles, narrow ? 1 : chunks);
-#define LAUNCH_ROWS(DVC, KEYS)                                                                           \
-    do {                                                                                                 \
-      if (prepare(latent_attention_rows_kernel<DVC, KEYS>, smem)) return 1;                              \
-      sprout_launch(latent_attention_rows_kernel<DVC, KEYS>, grid, dim3(THREADS), smem, stream, p);      \
+    const bool keys64 = (rows + 2 * 64) * row_bytes <= SMEM_LIMIT;
+    const size_t smem = (rows + 2 * (keys64 ? 64 : 32)) * row_bytes;
+    dim3 grid((unsigned)tiles, d.ctas);
+#define LAUNCH_ROWS(DVC, KEYS, CHUNKS)                                                                              \
+    do {                                                                                                            \
+      if (prepare(latent_attention_rows_kernel<DVC, KEYS, CHUNKS>)) return 1;                                       \
+      sprout_launch(latent_attention_rows_kernel<DVC, KEYS, CHUNKS>, grid, dim3(WARPS * 32), smem, stream, p);      \
     } while (0)
-    if (narrow) { if (keys64) LAUNCH_ROWS(128, 64); else LAUNCH_ROWS(128, 32); }
-    else { if (keys64) LAUNCH_ROWS(256, 64); else LAUNCH_ROWS(256, 32); }
+    if (d.dvc == 128) { if (keys64) LAUNCH_ROWS(128, 64, 1); else LAUNCH_ROWS(128, 32, 1); }
+    else if (d.chunks == 1) { if (keys64) LAUNCH_ROWS(256, 64, 1); else LAUNCH_ROWS(256, 32, 1); }
+    else { if (keys64) LAUNCH_ROWS(256, 64, 2); else LAUNCH_ROWS(256, 32, 2); }
 #undef LAUNCH_ROWS
     return sprout_check_launch("latent_attention_rows");
   }
   SPROUT_REQUIRE(tokens == requests && context_lens && scratch && split_keys > 0 && split_keys % 64 == 0,
                  "latent_attention_mma: split keys need one token per request, context lengths, scratch and ranges of a multiple of 64 keys");
-  // the stages' room is used again for the warps' partial sums: [4][16][DVC] floats
-  const size_t exchange = (size_t)4 * 16 * (narrow ? 128 : 256) * sizeof(float);
+  // the stages' room is used again for the warps' partial sums: [chunks][4][16][DVC] floats
+  const size_t exchange = (size_t)d.chunks * 4 * 16 * d.dvc * sizeof(float);
   const size_t smem = 16 * row_bytes + (2 * 64 * row_bytes > exchange ? 2 * 64 * row_bytes : exchange);
   SPROUT_REQUIRE(smem <= SMEM_LIMIT, "latent_attention_mma: rows too wide for the split kernel's shared memory");
-  const int groups = (heads + 15) / 16;
-  dim3 grid(requests * groups, narrow ? 1 : chunks, splits);
-  if (narrow) {
-    if (prepare(latent_attention_split_kernel<128>, smem)) return 1;
-    sprout_launch(latent_attention_split_kernel<128>, grid, dim3(THREADS), smem, stream, p);
-  } else {
-    if (prepare(latent_attention_split_kernel<256>, smem)) return 1;
-    sprout_launch(latent_attention_split_kernel<256>, grid, dim3(THREADS), smem, stream, p);
-  }
+  dim3 grid(requests * ((heads + 15) / 16), d.ctas, splits);
+#define LAUNCH_SPLIT(DVC, CHUNKS)                                                                                   \
+  do {                                                                                                              \
+    if (prepare(latent_attention_split_kernel<DVC, CHUNKS>)) return 1;                                              \
+    sprout_launch(latent_attention_split_kernel<DVC, CHUNKS>, grid, dim3(CHUNKS * 128), smem, stream, p);           \
+  } while (0)
+  if (d.dvc == 128) LAUNCH_SPLIT(128, 1);
+  else if (d.chunks == 1) LAUNCH_SPLIT(256, 1);
+  else LAUNCH_SPLIT(256, 2);
+#undef LAUNCH_SPLIT
   if (int code = sprout_check_launch("latent_attention_split")) return code;
   sprout_launch(latent_attention_merge_kernel, dim3(requests, heads), dim3(128), 0, stream, p);
   return sprout_check_launch("latent_attention_merge");

@@ -980,13 +980,18 @@ def latent_attention_mma_supported(width: int, rank: int) -> bool:
     return bool(lib.sprout_latent_attention_mma_supported(int(width), int(rank)))
 
 
-def latent_split_plan(requests: int, heads: int, rank: int, planned_keys: int) -> tuple[int, int]:
-    """(ranges, keys per range) for a step of one token per request: enough CTAs for two per SM, ranges of
-    a multiple of 64 keys, at most 64 of them.  It follows the contexts' length alone, so a captured
-    step is replayed for steps that plan alike."""
-    groups, chunks = -(-heads // 16), 1 if rank <= 128 else -(-rank // 256)
+def latent_split_plan(requests: int, heads: int, rank: int, planned_keys: int, width: int = 0) -> tuple[int, int]:
+    """(ranges, keys per range) for a step of one token per request: as many CTAs as the SMs hold at once
+    (one per SM for wide rows, whose two stages fill its shared memory), ranges of a multiple of 64 keys, at
+    most 64 of them.  It follows the contexts' length alone, so a captured step is replayed for steps that
+    plan alike."""
+    groups, along_y = -(-heads // 16), 1 if rank <= 512 else -(-rank // 512)
+    row_bytes = (max(width, rank) + 8) * 2
+    blocks = 1 if rank <= 256 else 2
+    shared = 16 * row_bytes + max(128 * row_bytes, blocks * 4 * 16 * (128 if rank <= 128 else 256) * 4)
+    per_sm = max(1, min(4, 227 * 1024 // (shared + 2048)))
     stages = max(1, -(-planned_keys // 64))
-    splits = max(1, min(2 * sm_count() // max(1, requests * groups * chunks), stages, 64))
+    splits = max(1, min(per_sm * sm_count() // max(1, requests * groups * along_y), stages, 64))
     split_keys = -(-stages // splits) * 64
     return -(-stages * 64 // split_keys), split_keys
 
@@ -1033,7 +1038,7 @@ def latent_attention(qlat, cache, ctx, sink, out, heads: int, rank: int, scale: 
                                        scale, status)
     splits = split_keys = 0
     if ctx.max_q_len == 1:
-        splits, split_keys = latent_split_plan(ctx.num_seqs, heads, rank, ctx.planned_context or ctx.max_context)
+        splits, split_keys = latent_split_plan(ctx.num_seqs, heads, rank, ctx.planned_context or ctx.max_context, width)
     latent_attention_mma(qlat, cache.k, cache.block_table, ctx.q_start, ctx.positions, ctx.context_lens, sink, out, heads, rank,
                          scale, status, ctx.num_seqs, splits, split_keys)
 

@@ -55,7 +55,7 @@ class LatentAttention(Part):
 
     def decode_plan(self, requests: int, max_keys: int, planned_context: int, page_tokens: int):
         """How a step of one token per request divides its keys among CTAs: it follows the contexts' length."""
-        return kernels.latent_split_plan(requests, self.heads, self.kv_rank, planned_context)
+        return kernels.latent_split_plan(requests, self.heads, self.kv_rank, planned_context, self.width)
 
     # ---- weights
     def tensor_decls(self):
