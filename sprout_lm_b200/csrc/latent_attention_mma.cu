@@ -16,6 +16,7 @@
 //    through shared memory; the ranges' partial sums go through float32 scratch to a merge kernel,
 //    which also adds the sink.
 #include "attention_bf16.cuh"
+#include "tcgen05.cuh"
 
 using namespace sprout_attn;
 
@@ -117,8 +118,10 @@ __device__ __forceinline__ void attend_block(const __nv_bfloat16* sQ, const __nv
   const float alpha1 = m1 == -INFINITY ? 0.f : exp2f(m1 * scale_log2 - base1);
   m0 = n0; m1 = n1;
   l0 *= alpha0; l1 *= alpha1;
+  if (!__all_sync(0xffffffffu, alpha0 == 1.f && alpha1 == 1.f)) {       // most blocks move no row's maximum
 #pragma unroll
-  for (int i = 0; i < DVC / 8; i++) { o[i][0] *= alpha0; o[i][1] *= alpha0; o[i][2] *= alpha1; o[i][3] *= alpha1; }
+    for (int i = 0; i < DVC / 8; i++) { o[i][0] *= alpha0; o[i][1] *= alpha0; o[i][2] *= alpha1; o[i][3] *= alpha1; }
+  }
 #pragma unroll
   for (int i = 0; i < NT; i++) {
     s[i][0] = exp2f(fmaf(s[i][0], scale_log2, -base0)); s[i][1] = exp2f(fmaf(s[i][1], scale_log2, -base0));
@@ -146,10 +149,16 @@ __device__ __forceinline__ void attend_block(const __nv_bfloat16* sQ, const __nv
   }
 }
 
-// Offsets of a stage's key rows (by the first KEYS threads), then their copy into shared memory.
+// One stage of key rows: each of the first KEYS threads finds its row's place in the pool and starts one bulk copy
+// of the whole row into shared memory (a row beyond the range is cleared instead); every one of them arrives on the
+// stage's mbarrier (initialised with a count of KEYS), a copying thread together with its row's bytes.
+__device__ __forceinline__ void bulk_row(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
 template <int KEYS>
-__device__ __forceinline__ void find_rows(const LatentParams& p, const int* table, int first_key, int last_key,
-                                          long long* offsets, int tid) {
+__device__ __forceinline__ void issue_stage(const LatentParams& p, const int* table, int first_key, int last_key,
+                                            __nv_bfloat16* dst, int stride, uint64_t* bar, int tid) {
   if (tid < KEYS) {
     const int key = first_key + tid;
     long long off = -1;
@@ -158,8 +167,22 @@ __device__ __forceinline__ void find_rows(const LatentParams& p, const int* tabl
       if (page < 0 || page >= p.num_pages) atomicOr(p.status, SPROUT_STATUS_BAD_PAGE);
       else off = ((long long)page * p.page_tokens + key % p.page_tokens) * p.width;
     }
-    offsets[tid] = off;
+    __nv_bfloat16* d = dst + tid * stride;
+    if (off >= 0) {
+      mbar_expect_tx(bar, (uint32_t)p.width * 2);
+      bulk_row(d, p.cache + off, (uint32_t)p.width * 2, bar);
+    } else {
+      for (int c = 0; c < p.width / 8; c++) ((uint4*)d)[c] = make_uint4(0, 0, 0, 0);
+      mbar_arrive(bar);
+    }
   }
+}
+// All threads wait for a stage.  A wait that runs out flags the status word and the CTA's `failed` flag, which every
+// thread reads after the next barrier: the CTA then stops walking keys, all its threads at the same stage.
+__device__ __forceinline__ void stage_landed(uint64_t* bar, uint32_t parity, int* status, volatile int* failed) {
+  if (mbar_wait(bar, parity)) return;
+  *failed = 1;
+  atomicOr(status, SPROUT_STATUS_WAIT_TIMEOUT);
 }
 // rows [0, rows) of 16-byte pieces: thread tid takes pieces tid, tid + threads, ... (row and piece advance without a division)
 template <typename F>
@@ -172,17 +195,6 @@ __device__ __forceinline__ void for_pieces(int rows, int pieces, int tid, int th
     if (c >= pieces) { c -= pieces; row++; }
   }
 }
-template <int KEYS>
-__device__ __forceinline__ void load_stage(const LatentParams& p, const long long* offsets, __nv_bfloat16* dst, int stride,
-                                           int tid, int threads) {
-  for_pieces(KEYS, p.width / 8, tid, threads, [&](int row, int c) {
-    const long long off = offsets[row];
-    __nv_bfloat16* d = dst + row * stride + c * 8;
-    if (off >= 0) cp_async16(d, p.cache + off + c * 8);
-    else *(uint4*)d = make_uint4(0, 0, 0, 0);
-  });
-}
-
 // ------------------------------------------------------------------------------ whole rows
 template <int DVC, int KEYS, int CHUNKS>
 __global__ void __launch_bounds__(WARPS * 32)
@@ -195,11 +207,18 @@ latent_attention_rows_kernel(const LatentParams p) {
   __shared__ int s_limit[ROWS];
   __shared__ int s_token[ROWS];
   __shared__ int s_head[ROWS];
-  __shared__ long long s_off[2][KEYS];
+  __shared__ __align__(8) uint64_t s_bar[2];
+  __shared__ int s_failed;
 
   pdl_launch_dependents();
-  pdl_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) {
+    s_failed = 0;
+    mbar_init(&s_bar[0], KEYS);
+    mbar_init(&s_bar[1], KEYS);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  pdl_wait();
   const int group = warp % GROUPS;                    // which 16 rows
   const int col0 = (blockIdx.y * CHUNKS + warp / GROUPS) * DVC, col_end = min(p.rank, col0 + DVC);
 
@@ -234,10 +253,9 @@ latent_attention_rows_kernel(const LatentParams p) {
     if (s_token[row] >= 0) cp_async16(dst, p.q + ((size_t)s_token[row] * p.heads + s_head[row]) * p.width + c * 8);
     else *(uint4*)dst = make_uint4(0, 0, 0, 0);
   });
-  find_rows<KEYS>(p, table, 0, max_limit, s_off[0], tid);
-  __syncthreads();
-  load_stage<KEYS>(p, s_off[0], sK, stride, tid, THREADS);
   cp_async_commit();
+  issue_stage<KEYS>(p, table, 0, max_limit, sK, stride, &s_bar[0], tid);
+  cp_async_wait<0>();                                 // this thread's pieces of the query rows; the loop's first barrier publishes them
 
   const int gr = lane >> 2, qc = lane & 3;
   const int my_row0 = group * 16 + gr, my_row1 = my_row0 + 8;
@@ -258,18 +276,15 @@ latent_attention_rows_kernel(const LatentParams p) {
 
   for (int t = 0; t < stages; t++) {
     const int buf = t & 1;
-    if (t + 1 < stages) find_rows<KEYS>(p, table, (t + 1) * KEYS, max_limit, s_off[buf ^ 1], tid);
-    __syncthreads();
-    if (t + 1 < stages) load_stage<KEYS>(p, s_off[buf ^ 1], sK + (buf ^ 1) * KEYS * stride, stride, tid, THREADS);
-    cp_async_commit();
-    cp_async_wait<1>();
-    __syncthreads();
+    __syncthreads();                                  // every warp is done with the other buffer; cleared rows are visible
+    if (s_failed) break;
+    if (t + 1 < stages) issue_stage<KEYS>(p, table, (t + 1) * KEYS, max_limit, sK + (buf ^ 1) * KEYS * stride, stride, &s_bar[buf ^ 1], tid);
+    stage_landed(&s_bar[buf], (t >> 1) & 1, p.status, &s_failed);
     const int key0 = t * KEYS;
     if (active && key0 <= warp_limit)
       attend_block<DVC, KEYS / 8>(sQ + group * 16 * stride, sK + buf * KEYS * stride, stride, p.width, col0, col_end, key0,
                                   limit0, limit1, key0 + KEYS - 1 > warp_min_limit, scale_log2, m0, m1, l0, l1, o, lane);
   }
-  cp_async_wait<0>();
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
   if (!active) return;
@@ -295,12 +310,19 @@ latent_attention_split_kernel(const LatentParams p) {
   const int stride = p.width + 8;
   __nv_bfloat16* sQ = (__nv_bfloat16*)lsm;            // [16][stride]
   __nv_bfloat16* sK = sQ + 16 * stride;               // [2][KEYS][stride]; after the loop: the warps' partial sums
-  __shared__ long long s_off[2][KEYS];
+  __shared__ __align__(8) uint64_t s_bar[2];
+  __shared__ int s_failed;
   __shared__ float s_ml[4][16][2];
 
   pdl_launch_dependents();
-  pdl_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) {
+    s_failed = 0;
+    mbar_init(&s_bar[0], KEYS);
+    mbar_init(&s_bar[1], KEYS);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  pdl_wait();
   const int quarter = warp & 3, chunk = warp >> 2;    // which 16 keys of a stage, which block of value columns
   const int groups = (p.heads + 15) / 16;
   const int r = blockIdx.x / groups, head0 = (blockIdx.x % groups) * 16;
@@ -318,10 +340,10 @@ latent_attention_split_kernel(const LatentParams p) {
     if (head0 + row < p.heads) cp_async16(dst, p.q + ((size_t)token * p.heads + head0 + row) * p.width + c * 8);
     else *(uint4*)dst = make_uint4(0, 0, 0, 0);
   });
-  if (stages > 0) find_rows<KEYS>(p, table, first, last, s_off[0], tid);
-  __syncthreads();
-  if (stages > 0) load_stage<KEYS>(p, s_off[0], sK, stride, tid, THREADS);
   cp_async_commit();
+  __syncthreads();                                    // the mbarriers are initialised
+  if (stages > 0) issue_stage<KEYS>(p, table, first, last, sK, stride, &s_bar[0], tid);
+  cp_async_wait<0>();
 
   const int gr = lane >> 2, qc = lane & 3;
   const float scale_log2 = p.scale * 1.4426950408889634f;
@@ -331,18 +353,15 @@ latent_attention_split_kernel(const LatentParams p) {
   for (int i = 0; i < DVC / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   for (int t = 0; t < stages; t++) {
     const int buf = t & 1;
-    if (t + 1 < stages) find_rows<KEYS>(p, table, first + (t + 1) * KEYS, last, s_off[buf ^ 1], tid);
-    __syncthreads();
-    if (t + 1 < stages) load_stage<KEYS>(p, s_off[buf ^ 1], sK + (buf ^ 1) * KEYS * stride, stride, tid, THREADS);
-    cp_async_commit();
-    cp_async_wait<1>();
-    __syncthreads();
+    __syncthreads();                                  // every warp is done with the other buffer; cleared rows are visible
+    if (s_failed) break;
+    if (t + 1 < stages) issue_stage<KEYS>(p, table, first + (t + 1) * KEYS, last, sK + (buf ^ 1) * KEYS * stride, stride, &s_bar[buf ^ 1], tid);
+    stage_landed(&s_bar[buf], (t >> 1) & 1, p.status, &s_failed);
     const int key0 = first + t * KEYS + quarter * 16; // this warp's quarter of the stage
     if (key0 <= last && col0 < p.rank)
       attend_block<DVC, 2>(sQ, sK + (buf * KEYS + quarter * 16) * stride, stride, p.width, col0, col_end, key0, last, last,
                            key0 + 15 > last, scale_log2, m0, m1, l0, l1, o, lane);
   }
-  cp_async_wait<0>();
   __syncthreads();                                    // every warp is done with the stages: they become the exchange area
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
