@@ -40,47 +40,49 @@ struct LatentParams {
   int* status;
 };
 
-// One warp: scores of its 16 rows against NT * 8 staged keys, online softmax, O += P V over the CTA's columns.
-template <int DVC, int NT>
-__device__ __forceinline__ void attend_block(const __nv_bfloat16* sQ, const __nv_bfloat16* tK, int stride, int width,
-                                             int col0, int col_end, int key0, int limit0, int limit1, bool mask,
-                                             float scale_log2, float& m0, float& m1, float& l0, float& l1,
-                                             float (&o)[DVC / 8][4], int lane) {
-  const int qc = lane & 3;
-  float s[NT][4];
+// One warp: scores of its 16 rows against NT * 8 staged keys over the k-steps [kk0, kk1) of the rows' width.
+template <int NT>
+__device__ __forceinline__ void scores_block(const __nv_bfloat16* sQ, const __nv_bfloat16* tK, int stride, int kk0, int kk1,
+                                             float (&s)[NT][4], int lane) {
 #pragma unroll
   for (int i = 0; i < NT; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
   const __nv_bfloat16* a_ptr = sQ + ((lane & 7) + ((lane >> 3) & 1) * 8) * stride + (lane >> 4) * 8;
   const __nv_bfloat16* b_ptr = tK + ((lane & 7) + (lane >> 4) * 8) * stride + ((lane >> 3) & 1) * 8;
   if (NT == 2) {
-    // one pair of tiles: even and odd k-steps go to accumulators of their own (two chains instead of one)
-    float s2[2][4];
-    s2[0][0] = s2[0][1] = s2[0][2] = s2[0][3] = s2[1][0] = s2[1][1] = s2[1][2] = s2[1][3] = 0.f;
-    const int steps = width / 16;
-#pragma unroll 2
-    for (int kk = 0; kk + 1 < steps; kk += 2) {
-      uint32_t a[4], b[4], a2[4], b2[4];
+    // one pair of tiles: four k-steps at a time go to accumulators of their own (four chains instead of one)
+    float c[3][2][4];
+#pragma unroll
+    for (int i = 0; i < 3; i++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) c[i][0][j] = c[i][1][j] = 0.f;
+    int kk = kk0;
+    for (; kk + 3 < kk1; kk += 4) {
+      uint32_t a[4][4], b[4][4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) { ldmatrix_x4(a[u], a_ptr + (kk + u) * 16); ldmatrix_x4(b[u], b_ptr + (kk + u) * 16); }
+      mma_bf16(s[0], a[0], b[0][0], b[0][1]);
+      mma_bf16(s[1], a[0], b[0][2], b[0][3]);
+#pragma unroll
+      for (int u = 1; u < 4; u++) {
+        mma_bf16(c[u - 1][0], a[u], b[u][0], b[u][1]);
+        mma_bf16(c[u - 1][1], a[u], b[u][2], b[u][3]);
+      }
+    }
+    for (; kk < kk1; kk++) {
+      uint32_t a[4], b[4];
       ldmatrix_x4(a, a_ptr + kk * 16);
       ldmatrix_x4(b, b_ptr + kk * 16);
-      ldmatrix_x4(a2, a_ptr + kk * 16 + 16);
-      ldmatrix_x4(b2, b_ptr + kk * 16 + 16);
-      mma_bf16(s[0], a, b[0], b[1]);
-      mma_bf16(s[1], a, b[2], b[3]);
-      mma_bf16(s2[0], a2, b2[0], b2[1]);
-      mma_bf16(s2[1], a2, b2[2], b2[3]);
-    }
-    if (steps & 1) {
-      uint32_t a[4], b[4];
-      ldmatrix_x4(a, a_ptr + (steps - 1) * 16);
-      ldmatrix_x4(b, b_ptr + (steps - 1) * 16);
       mma_bf16(s[0], a, b[0], b[1]);
       mma_bf16(s[1], a, b[2], b[3]);
     }
 #pragma unroll
-    for (int j = 0; j < 4; j++) { s[0][j] += s2[0][j]; s[1][j] += s2[1][j]; }
+    for (int j = 0; j < 4; j++) {
+      s[0][j] += (c[0][0][j] + c[1][0][j]) + c[2][0][j];
+      s[1][j] += (c[0][1][j] + c[1][1][j]) + c[2][1][j];
+    }
   } else {
 #pragma unroll 2
-    for (int kk = 0; kk < width / 16; kk++) {
+    for (int kk = kk0; kk < kk1; kk++) {
       uint32_t a[4];
       ldmatrix_x4(a, a_ptr + kk * 16);
 #pragma unroll
@@ -92,6 +94,14 @@ __device__ __forceinline__ void attend_block(const __nv_bfloat16* sQ, const __nv
       }
     }
   }
+}
+
+// The same warp, from its scores on: mask, online softmax, O += P V over the warp's value columns.
+template <int DVC, int NT>
+__device__ __forceinline__ void softmax_values_block(float (&s)[NT][4], const __nv_bfloat16* tK, int stride, int col0, int col_end,
+                                                     int key0, int limit0, int limit1, bool mask, float scale_log2, float& m0,
+                                                     float& m1, float& l0, float& l1, float (&o)[DVC / 8][4], int lane) {
+  const int qc = lane & 3;
   if (mask) {
 #pragma unroll
     for (int i = 0; i < NT; i++) {
@@ -147,6 +157,16 @@ __device__ __forceinline__ void attend_block(const __nv_bfloat16* sQ, const __nv
       }
     }
   }
+}
+
+template <int DVC, int NT>
+__device__ __forceinline__ void attend_block(const __nv_bfloat16* sQ, const __nv_bfloat16* tK, int stride, int width,
+                                             int col0, int col_end, int key0, int limit0, int limit1, bool mask,
+                                             float scale_log2, float& m0, float& m1, float& l0, float& l1,
+                                             float (&o)[DVC / 8][4], int lane) {
+  float s[NT][4];
+  scores_block<NT>(sQ, tK, stride, 0, width / 16, s, lane);
+  softmax_values_block<DVC, NT>(s, tK, stride, col0, col_end, key0, limit0, limit1, mask, scale_log2, m0, m1, l0, l1, o, lane);
 }
 
 // One stage of key rows: each of the first KEYS threads finds its row's place in the pool and starts one bulk copy
@@ -209,6 +229,8 @@ latent_attention_rows_kernel(const LatentParams p) {
   __shared__ int s_head[ROWS];
   __shared__ __align__(8) uint64_t s_bar[2];
   __shared__ int s_failed;
+  // with two blocks of value columns: a warp's partial scores, for the warp that has the same rows and the other block
+  __shared__ __align__(16) float s_part[CHUNKS == 2 ? WARPS : 1][CHUNKS == 2 ? KEYS * 16 : 4];
 
   pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -273,6 +295,7 @@ latent_attention_rows_kernel(const LatentParams p) {
   const int warp_min_limit = s_limit[min(group * 16, last_row)];
   const int warp_limit = s_limit[min(group * 16 + 15, last_row)];
   const bool active = group * 16 <= last_row && col0 < p.rank;
+  const bool paired = CHUNKS == 2 && (blockIdx.y * CHUNKS + 1) * DVC < p.rank;      // both blocks of value columns exist
 
   for (int t = 0; t < stages; t++) {
     const int buf = t & 1;
@@ -281,9 +304,31 @@ latent_attention_rows_kernel(const LatentParams p) {
     if (t + 1 < stages) issue_stage<KEYS>(p, table, (t + 1) * KEYS, max_limit, sK + (buf ^ 1) * KEYS * stride, stride, &s_bar[buf ^ 1], tid);
     stage_landed(&s_bar[buf], (t >> 1) & 1, p.status, &s_failed);
     const int key0 = t * KEYS;
-    if (active && key0 <= warp_limit)
-      attend_block<DVC, KEYS / 8>(sQ + group * 16 * stride, sK + buf * KEYS * stride, stride, p.width, col0, col_end, key0,
-                                  limit0, limit1, key0 + KEYS - 1 > warp_min_limit, scale_log2, m0, m1, l0, l1, o, lane);
+    if (active && key0 <= warp_limit) {
+      constexpr int NT = KEYS / 8;
+      const __nv_bfloat16* tK = sK + buf * KEYS * stride;
+      float sc[NT][4];
+      if (CHUNKS == 2 && paired) {
+        // the two warps with the same rows take half of the rows' width each and add their partial scores through
+        // shared memory: the scores are computed once per CTA, not once per block of value columns
+        const int steps = p.width / 16, half = (steps + 1) / 2;
+        scores_block<NT>(sQ + group * 16 * stride, tK, stride, warp >= GROUPS ? half : 0, warp >= GROUPS ? steps : half, sc, lane);
+        float4* mine = (float4*)s_part[CHUNKS == 2 ? warp : 0];
+#pragma unroll
+        for (int i = 0; i < NT; i++) mine[i * 32 + lane] = make_float4(sc[i][0], sc[i][1], sc[i][2], sc[i][3]);
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + group) : "memory");
+        const float4* other = (const float4*)s_part[CHUNKS == 2 ? (warp + GROUPS) % WARPS : 0];
+#pragma unroll
+        for (int i = 0; i < NT; i++) {
+          const float4 u = other[i * 32 + lane];
+          sc[i][0] += u.x; sc[i][1] += u.y; sc[i][2] += u.z; sc[i][3] += u.w;
+        }
+      } else {
+        scores_block<NT>(sQ + group * 16 * stride, tK, stride, 0, p.width / 16, sc, lane);
+      }
+      softmax_values_block<DVC, NT>(sc, tK, stride, col0, col_end, key0, limit0, limit1, key0 + KEYS - 1 > warp_min_limit,
+                                    scale_log2, m0, m1, l0, l1, o, lane);
+    }
   }
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
@@ -313,6 +358,7 @@ latent_attention_split_kernel(const LatentParams p) {
   __shared__ __align__(8) uint64_t s_bar[2];
   __shared__ int s_failed;
   __shared__ float s_ml[4][16][2];
+  __shared__ __align__(16) float s_part[CHUNKS * 4][256];   // a warp's partial scores, for the warp that shares its keys
 
   pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -347,6 +393,8 @@ latent_attention_split_kernel(const LatentParams p) {
 
   const int gr = lane >> 2, qc = lane & 3;
   const float scale_log2 = p.scale * 1.4426950408889634f;
+  const int steps = p.width / 16;
+  const bool paired = CHUNKS == 2 && cta_col0 + DVC < p.rank;          // both blocks of value columns exist
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
   float o[DVC / 8][4];
 #pragma unroll
@@ -358,9 +406,28 @@ latent_attention_split_kernel(const LatentParams p) {
     if (t + 1 < stages) issue_stage<KEYS>(p, table, first + (t + 1) * KEYS, last, sK + (buf ^ 1) * KEYS * stride, stride, &s_bar[buf ^ 1], tid);
     stage_landed(&s_bar[buf], (t >> 1) & 1, p.status, &s_failed);
     const int key0 = first + t * KEYS + quarter * 16; // this warp's quarter of the stage
-    if (key0 <= last && col0 < p.rank)
-      attend_block<DVC, 2>(sQ, sK + (buf * KEYS + quarter * 16) * stride, stride, p.width, col0, col_end, key0, last, last,
-                           key0 + 15 > last, scale_log2, m0, m1, l0, l1, o, lane);
+    if (key0 <= last && col0 < p.rank) {
+      const __nv_bfloat16* tK = sK + (buf * KEYS + quarter * 16) * stride;
+      float sc[2][4];
+      if (paired) {
+        // the two warps that hold the same keys (one per block of value columns) take half of the rows' width each
+        // and add their partial scores through shared memory
+        const int half = (steps + 1) / 2;
+        scores_block<2>(sQ, tK, stride, chunk ? half : 0, chunk ? steps : half, sc, lane);
+        float4* mine = (float4*)s_part[warp];
+        mine[lane] = make_float4(sc[0][0], sc[0][1], sc[0][2], sc[0][3]);
+        mine[32 + lane] = make_float4(sc[1][0], sc[1][1], sc[1][2], sc[1][3]);
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+        const float4* other = (const float4*)s_part[warp ^ 4];
+        const float4 u = other[lane], v = other[32 + lane];
+        sc[0][0] += u.x; sc[0][1] += u.y; sc[0][2] += u.z; sc[0][3] += u.w;
+        sc[1][0] += v.x; sc[1][1] += v.y; sc[1][2] += v.z; sc[1][3] += v.w;
+      } else {
+        scores_block<2>(sQ, tK, stride, 0, steps, sc, lane);
+      }
+      softmax_values_block<DVC, 2>(sc, tK, stride, col0, col_end, key0, last, last, key0 + 15 > last, scale_log2, m0, m1, l0, l1,
+                                   o, lane);
+    }
   }
   __syncthreads();                                    // every warp is done with the stages: they become the exchange area
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -421,17 +488,26 @@ latent_attention_merge_kernel(const LatentParams p) {
   }
 }
 
-constexpr size_t SMEM_LIMIT = 232448 - 4096;          // dynamic bytes a CTA may ask for beside the kernels' static arrays
+// dynamic bytes a CTA may ask for beside the kernels' static arrays (the split kernel's hold the warps' partial scores)
+constexpr size_t ROWS_LIMIT = 232448 - 2048, SPLIT_LIMIT = 232448 - 10240;
 
+// Raise a kernel's dynamic shared memory limit to what the SM has left beside the kernel's static arrays (once per
+// kernel), and refuse a launch that wants more.
 template <typename K>
-int prepare(K kernel) {
+int prepare(K kernel, size_t smem) {
   static thread_local const void* done[32];
+  static thread_local size_t room[32];
   static thread_local int count = 0;
-  for (int i = 0; i < count; i++) if (done[i] == (const void*)kernel) return 0;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT) != cudaSuccess)
+  for (int i = 0; i < count; i++)
+    if (done[i] == (const void*)kernel)
+      return smem <= room[i] ? 0 : sprout_fail("latent_attention: %zu bytes of shared memory wanted, %zu available", smem, room[i]);
+  cudaFuncAttributes attributes;
+  if (cudaFuncGetAttributes(&attributes, kernel) != cudaSuccess) return sprout_fail("latent_attention: cannot read the kernel's attributes");
+  const size_t available = 232448 - attributes.sharedSizeBytes;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)available) != cudaSuccess)
     return sprout_fail("latent_attention: cannot raise the kernel's shared memory limit");
-  if (count < 32) done[count++] = (const void*)kernel;
-  return 0;
+  if (count < 32) { done[count] = (const void*)kernel; room[count++] = available; }
+  return smem <= available ? 0 : sprout_fail("latent_attention: %zu bytes of shared memory wanted, %zu available", smem, available);
 }
 
 // How a latent of `rank` columns is divided: DVC columns per warp, `chunks` such blocks per CTA, CTAs along y.
@@ -449,7 +525,7 @@ SPROUT_API int sprout_latent_attention_mma_supported(int width, int rank) {
   if (width % 16 || rank % 16 || rank <= 0 || width < rank) return 0;
   const size_t row_bytes = (size_t)(width + 8) * 2;
   const int rows = 16 * WARPS / divide(rank).chunks;
-  return (rows + 2 * 32) * row_bytes <= SMEM_LIMIT && (16 + 2 * 64) * row_bytes <= SMEM_LIMIT;
+  return (rows + 2 * 32) * row_bytes + (divide(rank).chunks == 2 ? 32 * 512 : 0) <= ROWS_LIMIT && (16 + 2 * 64) * row_bytes <= SPLIT_LIMIT;
 }
 
 // splits == 0: whole rows (any mix of portions and single tokens).  splits >= 1: every request brings one token
@@ -477,17 +553,20 @@ SPROUT_API int sprout_latent_attention_mma(const void* q, const void* cache, con
     const int rows = 16 * WARPS / d.chunks;
     const long long tiles = ((long long)tokens * heads + rows - 1) / rows + requests;
     SPROUT_REQUIRE(tiles <= 0x7fffffffLL, "latent_attention_mma: too many rows");
-    const bool keys64 = (rows + 2 * 64) * row_bytes <= SMEM_LIMIT;
-    const size_t smem = (rows + 2 * (keys64 ? 64 : 32)) * row_bytes;
+    // stages of 64 keys where they fit, else 32; with two blocks of value columns 48 or 32 (the partial scores of 8 warps
+    // take KEYS x 512 bytes of static shared memory)
+    const bool keys64 = d.chunks == 1 && (rows + 2 * 64) * row_bytes <= ROWS_LIMIT;
+    const bool keys48 = d.chunks == 2 && (rows + 2 * 48) * row_bytes + 48 * 512 <= ROWS_LIMIT;
+    const size_t smem = (rows + 2 * (keys64 ? 64 : keys48 ? 48 : 32)) * row_bytes;
     dim3 grid((unsigned)tiles, d.ctas);
 #define LAUNCH_ROWS(DVC, KEYS, CHUNKS)                                                                              \
     do {                                                                                                            \
-      if (prepare(latent_attention_rows_kernel<DVC, KEYS, CHUNKS>)) return 1;                                       \
+      if (prepare(latent_attention_rows_kernel<DVC, KEYS, CHUNKS>, smem)) return 1;                                       \
       sprout_launch(latent_attention_rows_kernel<DVC, KEYS, CHUNKS>, grid, dim3(WARPS * 32), smem, stream, p);      \
     } while (0)
     if (d.dvc == 128) { if (keys64) LAUNCH_ROWS(128, 64, 1); else LAUNCH_ROWS(128, 32, 1); }
     else if (d.chunks == 1) { if (keys64) LAUNCH_ROWS(256, 64, 1); else LAUNCH_ROWS(256, 32, 1); }
-    else { if (keys64) LAUNCH_ROWS(256, 64, 2); else LAUNCH_ROWS(256, 32, 2); }
+    else { if (keys48) LAUNCH_ROWS(256, 48, 2); else LAUNCH_ROWS(256, 32, 2); }
 #undef LAUNCH_ROWS
     return sprout_check_launch("latent_attention_rows");
   }
@@ -496,11 +575,11 @@ SPROUT_API int sprout_latent_attention_mma(const void* q, const void* cache, con
   // the stages' room is used again for the warps' partial sums: [chunks][4][16][DVC] floats
   const size_t exchange = (size_t)d.chunks * 4 * 16 * d.dvc * sizeof(float);
   const size_t smem = 16 * row_bytes + (2 * 64 * row_bytes > exchange ? 2 * 64 * row_bytes : exchange);
-  SPROUT_REQUIRE(smem <= SMEM_LIMIT, "latent_attention_mma: rows too wide for the split kernel's shared memory");
+  SPROUT_REQUIRE(smem <= SPLIT_LIMIT, "latent_attention_mma: rows too wide for the split kernel's shared memory");
   dim3 grid(requests * ((heads + 15) / 16), d.ctas, splits);
 #define LAUNCH_SPLIT(DVC, CHUNKS)                                                                                   \
   do {                                                                                                              \
-    if (prepare(latent_attention_split_kernel<DVC, CHUNKS>)) return 1;                                              \
+    if (prepare(latent_attention_split_kernel<DVC, CHUNKS>, smem)) return 1;                                              \
     sprout_launch(latent_attention_split_kernel<DVC, CHUNKS>, grid, dim3(CHUNKS * 128), smem, stream, p);           \
   } while (0)
   if (d.dvc == 128) LAUNCH_SPLIT(128, 1);
