@@ -90,6 +90,96 @@ polynorm_kernel(const TI* __restrict__ z, TO* __restrict__ out, const float* __r
   }
 }
 
+// Rows whose width is a multiple of 4 and at most 256 x 4 x VEC: the row stays in registers between the sums and
+// the output (one read), 16-byte accesses.
+template <typename TO>
+__device__ __forceinline__ void store4(TO* dst, int i, float a, float b, float c, float d) {
+  if (sizeof(TO) == 4) {
+    ((float4*)dst)[i] = make_float4(a, b, c, d);
+  } else {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    ((uint2*)dst)[i] = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+  }
+}
+
+template <typename TO, int VEC>
+__global__ void __launch_bounds__(256)
+sum_norm_vec_kernel(const float* y, const float* __restrict__ gain, float* x, float* y2, TO* __restrict__ h,
+                    int hidden, float eps, float alpha) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t row = (size_t)blockIdx.x * hidden;
+  const int quads = hidden >> 2;
+  float4 v[VEC];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VEC; k++) {
+    const int i = threadIdx.x + k * 256;
+    v[k] = i < quads ? ((const float4*)(y + row))[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    ss += (v[k].x * v[k].x + v[k].y * v[k].y) + (v[k].z * v[k].z + v[k].w * v[k].w);
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+#pragma unroll
+  for (int k = 0; k < VEC; k++) {
+    const int i = threadIdx.x + k * 256;
+    if (i < quads) {
+      const float4 g = ((const float4*)gain)[i];
+      const float a = (v[k].x * scale) * g.x, b = (v[k].y * scale) * g.y, c = (v[k].z * scale) * g.z, d = (v[k].w * scale) * g.w;
+      ((float4*)(x + row))[i] = make_float4(a, b, c, d);
+      if (y2) ((float4*)(y2 + row))[i] = make_float4(alpha * a, alpha * b, alpha * c, alpha * d);
+      if (h) store4<TO>(h + row, i, a, b, c, d);
+    }
+  }
+}
+
+template <typename TO, int VEC>
+__global__ void __launch_bounds__(256)
+polynorm_vec_kernel(const float* __restrict__ z, TO* __restrict__ out, const float* __restrict__ coef, int width, float eps) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t row = (size_t)blockIdx.x * width;
+  const int quads = width >> 2;
+  float4 v[VEC];
+  float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+#pragma unroll
+  for (int k = 0; k < VEC; k++) {
+    const int i = threadIdx.x + k * 256;
+    v[k] = i < quads ? ((const float4*)(z + row))[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float e[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const float p2 = e[j] * e[j], p3 = p2 * e[j];
+      s2 = fmaf(e[j], e[j], s2);
+      s4 = fmaf(p2, p2, s4);
+      s6 = fmaf(p3, p3, s6);
+    }
+  }
+  s2 = block_sum(s2, scratch);
+  s4 = block_sum(s4, scratch);
+  s6 = block_sum(s6, scratch);
+  const float r1 = 1.0f / sqrtf(s2 / (float)width + eps);
+  const float r2 = 1.0f / sqrtf(s4 / (float)width + eps);
+  const float r3 = 1.0f / sqrtf(s6 / (float)width + eps);
+  const float a = coef[0], b = coef[1], c = coef[2], e0 = coef[3];
+#pragma unroll
+  for (int k = 0; k < VEC; k++) {
+    const int i = threadIdx.x + k * 256;
+    if (i < quads) {
+      const float e[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+      float r[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const float p2 = e[j] * e[j], p3 = p2 * e[j];
+        r[j] = a * (e[j] * r1) + b * (p2 * r2) + c * (p3 * r3) + e0;
+      }
+      store4<TO>(out + row, i, r[0], r[1], r[2], r[3]);
+    }
+  }
+}
+
 // ---------------------------------------------------------------- latent_kv_append
 // src row t (float32, row stride ld): [rank latent values | rot shared key values].  The cache
 // row of token t: page = table[seq][pos / page_tokens], slot pos % page_tokens, `rank + rot` wide.
@@ -392,6 +482,24 @@ __global__ void depth_average_kernel(float* __restrict__ history, float* __restr
   }
 }
 
+__global__ void depth_average_vec_kernel(float4* __restrict__ history, float4* __restrict__ x, const float* __restrict__ w,
+                                         int n, long long plane4) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < plane4; i += (long long)gridDim.x * blockDim.x) {
+    const float4 latest = x[i];
+    history[(long long)(n + 1) * plane4 + i] = latest;
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j <= n; j++) {
+      const float4 v = history[(long long)j * plane4 + i];
+      const float wj = w[j];
+      sum.x = fmaf(wj, v.x, sum.x); sum.y = fmaf(wj, v.y, sum.y); sum.z = fmaf(wj, v.z, sum.z); sum.w = fmaf(wj, v.w, sum.w);
+    }
+    const float wl = w[n + 1];
+    x[i] = make_float4(fmaf(wl, latest.x, sum.x), fmaf(wl, latest.y, sum.y), fmaf(wl, latest.z, sum.z), fmaf(wl, latest.w, sum.w));
+  }
+}
+
 __global__ void softcap_kernel(float* __restrict__ x, float cap, long long count) {
   pdl_launch_dependents();
   pdl_wait();
@@ -420,6 +528,16 @@ SPROUT_API int sprout_scale_cast(const float* x, float* y, void* h, int h_dtype,
 SPROUT_API int sprout_sum_norm(const float* y, const float* gain, float* x, float* y2, void* h, int h_dtype, int rows,
                                int hidden, float eps, float alpha, cudaStream_t stream) {
   SPROUT_REQUIRE(y && gain && x && rows > 0 && hidden > 0, "sum_norm: null pointer or empty");
+  const bool aligned = hidden % 4 == 0 && hidden <= 8192 && (((uintptr_t)y | (uintptr_t)gain | (uintptr_t)x | (uintptr_t)y2 | (uintptr_t)h) & 15) == 0;
+  if (aligned) {
+#define SUM_NORM_VEC(TO, VEC) sprout_launch(sum_norm_vec_kernel<TO, VEC>, dim3(rows), dim3(256), 0, stream, y, gain, x, y2, (TO*)h, hidden, eps, alpha)
+#define SUM_NORM_PICK(TO) do { if (hidden <= 1024) SUM_NORM_VEC(TO, 1); else if (hidden <= 2048) SUM_NORM_VEC(TO, 2); \
+                               else if (hidden <= 4096) SUM_NORM_VEC(TO, 4); else SUM_NORM_VEC(TO, 8); } while (0)
+    if (h && h_dtype == SPROUT_BF16) SUM_NORM_PICK(__nv_bfloat16); else SUM_NORM_PICK(float);
+#undef SUM_NORM_PICK
+#undef SUM_NORM_VEC
+    return sprout_check_launch("sum_norm");
+  }
   if (h && h_dtype == SPROUT_BF16)
     sprout_launch(sum_norm_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, stream, y, gain, x, y2, (__nv_bfloat16*)h, hidden, eps, alpha);
   else
@@ -430,6 +548,16 @@ SPROUT_API int sprout_sum_norm(const float* y, const float* gain, float* x, floa
 SPROUT_API int sprout_polynorm(const void* z, int z_dtype, void* out, int out_dtype, const float* coef, int rows, int width,
                                float eps, cudaStream_t stream) {
   SPROUT_REQUIRE(z && out && coef && rows > 0 && width > 0, "polynorm: null pointer or empty");
+  if (z_dtype == SPROUT_F32 && width % 4 == 0 && width <= 8192 && (((uintptr_t)z | (uintptr_t)out) & 15) == 0 &&
+      (out_dtype == SPROUT_F32 || out_dtype == SPROUT_BF16)) {
+#define POLY_VEC(TO, VEC) sprout_launch(polynorm_vec_kernel<TO, VEC>, dim3(rows), dim3(256), 0, stream, (const float*)z, (TO*)out, coef, width, eps)
+#define POLY_PICK(TO) do { if (width <= 1024) POLY_VEC(TO, 1); else if (width <= 2048) POLY_VEC(TO, 2); \
+                           else if (width <= 4096) POLY_VEC(TO, 4); else POLY_VEC(TO, 8); } while (0)
+    if (out_dtype == SPROUT_BF16) POLY_PICK(__nv_bfloat16); else POLY_PICK(float);
+#undef POLY_PICK
+#undef POLY_VEC
+    return sprout_check_launch("polynorm");
+  }
   if (z_dtype == SPROUT_F32 && out_dtype == SPROUT_F32)
     sprout_launch(polynorm_kernel<float, float>, dim3(rows), dim3(256), 0, stream, (const float*)z, (float*)out, coef, width, eps);
   else if (z_dtype == SPROUT_F32 && out_dtype == SPROUT_BF16)
@@ -532,7 +660,11 @@ SPROUT_API int sprout_latent_attention_simple(const void* qlat, const void* cach
 
 SPROUT_API int sprout_depth_average(float* history, float* x, const float* weights, int n, long long plane, cudaStream_t stream) {
   SPROUT_REQUIRE(history && x && weights && n >= 0 && plane > 0, "depth_average: null pointer or sizes");
-  sprout_launch(depth_average_kernel, dim3(flat_grid(plane, 256)), dim3(256), 0, stream, history, x, weights, n, plane);
+  if (plane % 4 == 0 && (((uintptr_t)history | (uintptr_t)x) & 15) == 0)
+    sprout_launch(depth_average_vec_kernel, dim3(flat_grid(plane / 4, 256)), dim3(256), 0, stream, (float4*)history, (float4*)x, weights,
+                  n, plane / 4);
+  else
+    sprout_launch(depth_average_kernel, dim3(flat_grid(plane, 256)), dim3(256), 0, stream, history, x, weights, n, plane);
   return sprout_check_launch("depth_average");
 }
 

@@ -463,28 +463,37 @@ latent_attention_split_kernel(const LatentParams p) {
   }
 }
 
-// One block per (request, head): the ranges' partial sums and the sink become the output row.
+// One block per (request, head): the ranges' partial sums and the sink become the output row.  The ranges' weights
+// exp(m_s - top) / denominator are made once (shared memory, up to 64 ranges), then every column is one pass of
+// independent loads.
 __global__ void __launch_bounds__(128)
 latent_attention_merge_kernel(const LatentParams p) {
+  __shared__ float s_m[64], s_w[64];
   pdl_launch_dependents();
   pdl_wait();
-  const int r = blockIdx.x, h = blockIdx.y;
+  const int r = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const size_t base = ((size_t)r * p.splits) * p.heads + h;
+  if (tid < p.splits) s_m[tid] = p.part_ml[(base + (size_t)tid * p.heads) * 2];
+  __syncthreads();
   float top = p.sink ? p.sink[h] : -INFINITY;
-  for (int s = 0; s < p.splits; s++) top = fmaxf(top, p.part_ml[(((size_t)r * p.splits + s) * p.heads + h) * 2]);
+  for (int s = 0; s < p.splits; s++) top = fmaxf(top, s_m[s]);
+  if (tid < p.splits) s_w[tid] = s_m[tid] == -INFINITY ? 0.f : expf(s_m[tid] - top);
+  __syncthreads();
   float denom = p.sink ? expf(p.sink[h] - top) : 0.f;
-  for (int s = 0; s < p.splits; s++) {
-    const float* ml = p.part_ml + (((size_t)r * p.splits + s) * p.heads + h) * 2;
-    if (ml[0] != -INFINITY) denom = fmaf(expf(ml[0] - top), ml[1], denom);
+  if (tid < 32) {
+    float part = 0.f;
+    for (int s = tid; s < p.splits; s += 32) part = fmaf(s_w[s], p.part_ml[(base + (size_t)s * p.heads) * 2 + 1], part);
+    part = warp_sum(part);
+    if (tid == 0) s_m[0] = denom + part;
   }
+  __syncthreads();
+  const float inv = 1.0f / s_m[0];
   const int token = p.q_start[r];
-  for (int c = threadIdx.x; c < p.rank; c += blockDim.x) {
+  for (int c = tid; c < p.rank; c += blockDim.x) {
     float sum = 0.f;
-    for (int s = 0; s < p.splits; s++) {
-      const size_t at = ((size_t)r * p.splits + s) * p.heads + h;
-      const float m = p.part_ml[at * 2];
-      if (m != -INFINITY) sum = fmaf(expf(m - top), p.part_o[at * p.rank + c], sum);
-    }
-    p.out[((size_t)token * p.heads + h) * p.rank + c] = __float2bfloat16_rn(sum / denom);
+#pragma unroll 4
+    for (int s = 0; s < p.splits; s++) sum = fmaf(s_w[s], p.part_o[(base + (size_t)s * p.heads) * p.rank + c], sum);
+    p.out[((size_t)token * p.heads + h) * p.rank + c] = __float2bfloat16_rn(sum * inv);
   }
 }
 
@@ -570,6 +579,7 @@ SPROUT_API int sprout_latent_attention_mma(const void* q, const void* cache, con
 #undef LAUNCH_ROWS
     return sprout_check_launch("latent_attention_rows");
   }
+  SPROUT_REQUIRE(splits <= 64, "latent_attention_mma: at most 64 ranges of keys (got %d)", splits);
   SPROUT_REQUIRE(tokens == requests && context_lens && scratch && split_keys > 0 && split_keys % 64 == 0,
                  "latent_attention_mma: split keys need one token per request, context lengths, scratch and ranges of a multiple of 64 keys");
   // the stages' room is used again for the warps' partial sums: [chunks][4][16][DVC] floats

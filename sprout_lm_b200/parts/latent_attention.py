@@ -109,14 +109,14 @@ class LatentAttention(Part):
             raise RuntimeError("latent_attention: a layer with a down-projection of its own writes its cache slot, "
                                "a layer without one reads another layer's")
         if self.own_kv:
-            rows = self.dkv.forward(h, out_dtype=torch.float32)
+            rows = self.dkv.forward_float32(h)
             kernels.latent_kv_append(rows, self.dkv_gain, ctx.positions, ctx.seq_of_token, cache.block_table, cos, sin,
                                      self.interleaved, cache.k, self.kv_rank, self.eps, status)
         if self.q_rank is None:
             q = self.q.forward(h)
         else:
             cq = torch.empty((tokens, self.q_rank), dtype=h.dtype, device=h.device)
-            kernels.rmsnorm(self.dq.forward(h, out_dtype=torch.float32), self.dq_gain, cq, self.eps)
+            kernels.rmsnorm(self.dq.forward_float32(h), self.dq_gain, cq, self.eps)
             q = self.uq.forward(cq)
         q_lat = (torch.empty if self.dim else torch.zeros)((tokens, self.heads * self.width), dtype=h.dtype, device=h.device)
         if self.dim:

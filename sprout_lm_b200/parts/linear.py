@@ -78,6 +78,15 @@ class Linear:
         else:
             kernels.gemm_bf16(a, self.weight, acc, self.status, residual=acc, split_k=self.split_k(a.shape[0], True))
 
+    def forward_float32(self, a: torch.Tensor) -> torch.Tensor:
+        """a W^T as float32.  For few tokens of a bfloat16 matrix the product is split along K into a zeroed
+        buffer, so that every SM streams a share of the weights; otherwise ``forward``."""
+        if self.tensor_cores and a.shape[0] <= 256 and a.stride(0) % 8 == 0 and self.bias is None:
+            out = torch.zeros((a.shape[0], self.out_features), dtype=torch.float32, device=a.device)
+            self.accumulate(a, out)
+            return out
+        return self.forward(a, out_dtype=torch.float32)
+
     def accumulate_unscaled(self, norm, x: torch.Tensor, acc: torch.Tensor) -> bool:
         """acc += bfloat16(x * gain) W^T: the product of the norm's output without its scale, for a
         consumer that multiplies row m's sums by 1 / rms(x[m]) itself (decode attention does).  The

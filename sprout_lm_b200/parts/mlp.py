@@ -102,7 +102,7 @@ class PolyNormMLP(Part):
         self.coefficients = source.vector(self.names["act"])
 
     def forward(self, h, x, ctx=None):
-        z = self.up.forward(h, out_dtype=torch.float32)
+        z = self.up.forward_float32(h)
         act = torch.empty(z.shape, dtype=h.dtype, device=h.device)
         kernels.polynorm(z, act, self.coefficients, self.eps)
         self.down.forward(act, residual=x)
