@@ -1,8 +1,8 @@
 """Command line in the manner of the reference's demo (src/demo.ts) and smoke script
 (scripts/smoke-cuda.ts).
 
-    python -m sprout_lm_b200 demo [--model DIR | --tiny A|B] [--seed S] [--json] [--pressure] [--dtype bfloat16|float32]
-    python -m sprout_lm_b200 generate (--model DIR | --tiny A|B) --prompt 1,2,3 [--max-new-tokens N]
+    python -m sprout_lm_b200 demo [--model DIR | --tiny A|B|T] [--seed S] [--json] [--pressure] [--dtype bfloat16|float32]
+    python -m sprout_lm_b200 generate (--model DIR | --tiny A|B|T) --prompt 1,2,3 [--max-new-tokens N]
                                       [--temperature T] [--seed S] [--ignore-eos] [--json]
     python -m sprout_lm_b200 random-model --out DIR --config CONFIG.json [--seed S]
 
@@ -34,6 +34,26 @@ TINY = {
 DEMO_TINY = TINY["A"]
 
 
+def _latent_layer(kind, heads, dim, rot_dim, vdim, kv_rank, base, ff, **extra):
+    rot = {"base": base, "dims": rot_dim}
+    if kind == "latent_attention_2":
+        rot["scaling"] = {"factor": 4.0, "original": 128, "fast": 16.0, "slow": 1.0}
+    return {"type": kind, "mlp": {"kind": "dense", "ff": ff},
+            "mixer": {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank,
+                      "scale": (dim + rot_dim) ** -0.5, "rot": rot, **extra}}
+
+
+# --tiny T: a tiny random Tulipel model (latent attention; four layers, the third reads the rows the first cached)
+TINY_CONFIGS = {
+    "T": {"architecture": "Tulipel", "vocab": 384, "width": 128, "postln_alpha": 2.0, "logit_softcap": 20.0, "norm": {"eps": 1e-5},
+          "max_positions": 512,
+          "layers": [_latent_layer("latent_attention_2", 4, 16, 16, 24, 64, 10000.0, 256),
+                     _latent_layer("latent_attention", 2, 32, 16, 32, 48, 50000.0, 192, q_rank=64),
+                     _latent_layer("latent_attention_2", 4, 16, 16, 24, 64, 10000.0, 256, kv_from=0),
+                     _latent_layer("latent_attention", 2, 32, 16, 32, 48, 50000.0, 192, q_rank=64)]},
+}
+
+
 def _table(rows: list[dict]) -> str:
     if not rows:
         return "  (no work)"
@@ -50,8 +70,11 @@ def _load(args):
     if args.model:
         return load_model(args.model, dtype=args.dtype), None
     tmp = tempfile.TemporaryDirectory()
-    sizes = TINY[getattr(args, "tiny", None) or "A"]
-    config = parse_config({"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_act": "silu", **sizes})
+    name = getattr(args, "tiny", None) or "A"
+    if name in TINY_CONFIGS:
+        config = parse_config(TINY_CONFIGS[name])
+    else:
+        config = parse_config({"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_act": "silu", **TINY[name]})
     write_random_model(tmp.name, config, seed=args.seed)
     return load_model(tmp.name, dtype=args.dtype), tmp
 
@@ -176,8 +199,9 @@ def main(argv=None) -> int:
     gen.add_argument("--json", action="store_true")
     for p in (demo, gen):
         p.add_argument("--model", help="folder with config.json and model.safetensors")
-        p.add_argument("--tiny", choices=sorted(TINY), help="instead of --model: a tiny random model (A: 2 layers, hidden 64, "
-                       "4/2 heads of 16, tied head; B: 3 layers, hidden 96, 3/1 heads of 32, untied head), written with --seed")
+        p.add_argument("--tiny", choices=sorted(TINY) + sorted(TINY_CONFIGS), help="instead of --model: a tiny random model (A: 2 layers, "
+                       "hidden 64, 4/2 heads of 16, tied head; B: 3 layers, hidden 96, 3/1 heads of 32, untied head; T: a Tulipel "
+                       "model of 4 latent-attention layers, width 128), written with --seed")
         p.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
         p.add_argument("--seed", type=int, default=0)
     rnd = sub.add_parser("random-model", help="write config.json and model.safetensors with random weights")

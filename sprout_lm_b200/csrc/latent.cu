@@ -102,10 +102,12 @@ __device__ __forceinline__ void store4(TO* dst, int i, float a, float b, float c
   }
 }
 
+// With `history` ([entries, rows, hidden] float32): the normed row is kept as entry n + 1 and what goes on (x, y2, h) is
+// sum_{j <= n + 1} w[j] * history[j] of the row, in the order the separate depth_average kernel adds.
 template <typename TO, int VEC>
 __global__ void __launch_bounds__(256)
 sum_norm_vec_kernel(const float* y, const float* __restrict__ gain, float* x, float* y2, TO* __restrict__ h,
-                    int hidden, float eps, float alpha) {
+                    int hidden, float eps, float alpha, float* history, const float* __restrict__ w, int n, long long plane) {
   __shared__ float scratch[33];
   pdl_launch_dependents();
   pdl_wait();
@@ -126,7 +128,18 @@ sum_norm_vec_kernel(const float* y, const float* __restrict__ gain, float* x, fl
     const int i = threadIdx.x + k * 256;
     if (i < quads) {
       const float4 g = ((const float4*)gain)[i];
-      const float a = (v[k].x * scale) * g.x, b = (v[k].y * scale) * g.y, c = (v[k].z * scale) * g.z, d = (v[k].w * scale) * g.w;
+      float a = (v[k].x * scale) * g.x, b = (v[k].y * scale) * g.y, c = (v[k].z * scale) * g.z, d = (v[k].w * scale) * g.w;
+      if (history) {
+        ((float4*)(history + (long long)(n + 1) * plane + row))[i] = make_float4(a, b, c, d);
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j <= n; j++) {
+          const float4 e = ((const float4*)(history + (long long)j * plane + row))[i];
+          const float wj = w[j];
+          sum.x = fmaf(wj, e.x, sum.x); sum.y = fmaf(wj, e.y, sum.y); sum.z = fmaf(wj, e.z, sum.z); sum.w = fmaf(wj, e.w, sum.w);
+        }
+        const float wl = w[n + 1];
+        a = fmaf(wl, a, sum.x); b = fmaf(wl, b, sum.y); c = fmaf(wl, c, sum.z); d = fmaf(wl, d, sum.w);
+      }
       ((float4*)(x + row))[i] = make_float4(a, b, c, d);
       if (y2) ((float4*)(y2 + row))[i] = make_float4(alpha * a, alpha * b, alpha * c, alpha * d);
       if (h) store4<TO>(h + row, i, a, b, c, d);
@@ -525,12 +538,22 @@ SPROUT_API int sprout_scale_cast(const float* x, float* y, void* h, int h_dtype,
   return sprout_check_launch("scale_cast");
 }
 
+SPROUT_API int sprout_scale_cast(const float* x, float* y, void* h, int h_dtype, float alpha, long long count, cudaStream_t stream);
+SPROUT_API int sprout_depth_average(float* history, float* x, const float* weights, int n, long long plane, cudaStream_t stream);
+
+// x = rmsnorm(y) * gain; optionally y2 = alpha * x and h = x in h's dtype.  With `history` (float32 [entries, rows, hidden])
+// and `weights`: the normed rows become entry n + 1 of the history, and x (and y2, h) is the weighted sum of the entries
+// 0..n+1: the norm after a layer's last sum, the depth average and the next layer's readers in one launch.
 SPROUT_API int sprout_sum_norm(const float* y, const float* gain, float* x, float* y2, void* h, int h_dtype, int rows,
-                               int hidden, float eps, float alpha, cudaStream_t stream) {
+                               int hidden, float eps, float alpha, float* history, const float* weights, int n,
+                               cudaStream_t stream) {
   SPROUT_REQUIRE(y && gain && x && rows > 0 && hidden > 0, "sum_norm: null pointer or empty");
-  const bool aligned = hidden % 4 == 0 && hidden <= 8192 && (((uintptr_t)y | (uintptr_t)gain | (uintptr_t)x | (uintptr_t)y2 | (uintptr_t)h) & 15) == 0;
+  SPROUT_REQUIRE(!history || (weights && n >= 0), "sum_norm: a history comes with its weights");
+  const long long plane = (long long)rows * hidden;
+  const bool aligned = hidden % 4 == 0 && hidden <= 8192 &&
+                       (((uintptr_t)y | (uintptr_t)gain | (uintptr_t)x | (uintptr_t)y2 | (uintptr_t)h | (uintptr_t)history) & 15) == 0;
   if (aligned) {
-#define SUM_NORM_VEC(TO, VEC) sprout_launch(sum_norm_vec_kernel<TO, VEC>, dim3(rows), dim3(256), 0, stream, y, gain, x, y2, (TO*)h, hidden, eps, alpha)
+#define SUM_NORM_VEC(TO, VEC) sprout_launch(sum_norm_vec_kernel<TO, VEC>, dim3(rows), dim3(256), 0, stream, y, gain, x, y2, (TO*)h, hidden, eps, alpha, history, weights, n, plane)
 #define SUM_NORM_PICK(TO) do { if (hidden <= 1024) SUM_NORM_VEC(TO, 1); else if (hidden <= 2048) SUM_NORM_VEC(TO, 2); \
                                else if (hidden <= 4096) SUM_NORM_VEC(TO, 4); else SUM_NORM_VEC(TO, 8); } while (0)
     if (h && h_dtype == SPROUT_BF16) SUM_NORM_PICK(__nv_bfloat16); else SUM_NORM_PICK(float);
@@ -538,11 +561,18 @@ SPROUT_API int sprout_sum_norm(const float* y, const float* gain, float* x, floa
 #undef SUM_NORM_VEC
     return sprout_check_launch("sum_norm");
   }
-  if (h && h_dtype == SPROUT_BF16)
-    sprout_launch(sum_norm_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, stream, y, gain, x, y2, (__nv_bfloat16*)h, hidden, eps, alpha);
+  // rows that allow no 16-byte accesses: the plain kernel, and with a history the separate steps after it
+  float* y2_now = history ? nullptr : y2;
+  void* h_now = history ? nullptr : h;
+  if (h_now && h_dtype == SPROUT_BF16)
+    sprout_launch(sum_norm_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, stream, y, gain, x, y2_now, (__nv_bfloat16*)h_now, hidden, eps, alpha);
   else
-    sprout_launch(sum_norm_kernel<float>, dim3(rows), dim3(256), 0, stream, y, gain, x, y2, (float*)h, hidden, eps, alpha);
-  return sprout_check_launch("sum_norm");
+    sprout_launch(sum_norm_kernel<float>, dim3(rows), dim3(256), 0, stream, y, gain, x, y2_now, (float*)h_now, hidden, eps, alpha);
+  if (int code = sprout_check_launch("sum_norm")) return code;
+  if (!history) return 0;
+  if (int code = sprout_depth_average(history, x, weights, n, plane, stream)) return code;
+  if (y2) return sprout_scale_cast(x, y2, h, h_dtype, alpha, plane, stream);
+  return 0;
 }
 
 SPROUT_API int sprout_polynorm(const void* z, int z_dtype, void* out, int out_dtype, const float* coef, int rows, int width,

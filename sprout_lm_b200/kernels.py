@@ -52,7 +52,7 @@ _SIGNATURES = {
     "sprout_linear_decode": [_P, _I, _P, _P, _F, _P, _P, _I, _I, _I, _I, _P, _P],
     "sprout_linear_decode_supported": [_I, _I, _I],
     "sprout_scale_cast": [_P, _P, _P, _I, _F, _L, _P],
-    "sprout_sum_norm": [_P, _P, _P, _P, _P, _I, _I, _I, _F, _F, _P],
+    "sprout_sum_norm": [_P, _P, _P, _P, _P, _I, _I, _I, _F, _F, _P, _P, _I, _P],
     "sprout_polynorm": [_P, _I, _P, _I, _P, _I, _I, _F, _P],
     "sprout_latent_kv_append": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P],
     "sprout_latent_query_tail": [_P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
@@ -872,17 +872,24 @@ def scale_cast(x, y, h, alpha: float):
          _dtype_code(h.dtype) if h is not None else F32, float(alpha), x.numel(), _stream())
 
 
-def sum_norm(y, gain, x, eps: float, y2=None, h=None, alpha: float = 1.0):
+def sum_norm(y, gain, x, eps: float, y2=None, h=None, alpha: float = 1.0, history=None, weights=None, n: int = 0):
     """x = rmsnorm(y) * gain (float32; ``x`` may be ``y``); optionally y2 = alpha * x (may be ``y``)
-    and h = x in h's dtype, for the sublayer that follows."""
+    and h = x in h's dtype, for the sublayer that follows.  With ``history`` (float32 [entries, rows, hidden]) and
+    ``weights``: the normed rows become entry n + 1 of the history and x, y2 and h are made from
+    sum_{j <= n + 1} weights[j] * history[j] instead (``depth_average`` folded in)."""
     if y.dim() != 2 or not y.is_contiguous() or not x.is_contiguous() or x.shape != y.shape or gain.numel() != y.shape[1]:
         raise KernelError("sum_norm: y and x must be contiguous [rows, hidden], gain [hidden]")
     for name, t in (("y2", y2), ("h", h)):
         if t is not None and (t.shape != y.shape or not t.is_contiguous()):
             raise KernelError(f"sum_norm: {name} must be contiguous and have y's shape")
+    if history is not None and (history.dim() != 3 or not history.is_contiguous() or tuple(history.shape[1:]) != tuple(y.shape)
+                                or weights is None or not 0 <= n + 1 < history.shape[0] or weights.numel() < n + 2
+                                or (h is not None and y2 is None)):
+        raise KernelError("sum_norm: history must be contiguous [entries, rows, hidden] with n + 1 inside it and n + 2 weights")
     _run("sprout_sum_norm", _ptr(y, "y", torch.float32), _ptr(gain, "gain", torch.float32), _ptr(x, "x", torch.float32),
          _ptr(y2, "y2", torch.float32, True), _ptr(h, "h", allow_none=True), _dtype_code(h.dtype) if h is not None else F32,
-         y.shape[0], y.shape[1], float(eps), float(alpha), _stream())
+         y.shape[0], y.shape[1], float(eps), float(alpha), _ptr(history, "history", torch.float32, True),
+         _ptr(weights, "weights", torch.float32, True), int(n), _stream())
 
 
 def polynorm(z, out, coefficients, eps: float):

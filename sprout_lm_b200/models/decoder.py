@@ -112,10 +112,27 @@ class DecoderModel:
         (``cache.storage.CacheStorage``)."""
         x = self.embedding.forward(ctx.token_ids)
         carry = self.stream.begin(x, len(self.spec.order)) if self.stream else None
+        # a block that ends in a norm may hand that norm to the stream part, which then also fills what the next block reads
+        fuses = self.stream is not None and hasattr(self.stream, "norm_after")
+        primed = None
         for n, call in enumerate(self.spec.order):
             cache = storage.view(call.cache, ctx, write=call.writes_cache)
             state = storage.state_view(call.layer, ctx)
-            self.blocks[call.layer].forward(x, ctx, cache, state)
+            block = self.blocks[call.layer]
+            if fuses and hasattr(block, "readers"):
+                following = self.blocks[self.spec.order[n + 1].layer] if n + 1 < len(self.spec.order) else None
+                ahead = following.readers(x) if following is not None and hasattr(following, "readers") else None
+
+                def finish(y, gain, eps, n=n, ahead=ahead, following=following):
+                    if ahead is None:
+                        self.stream.norm_after(carry, n, y, gain, eps, x)
+                    else:
+                        self.stream.norm_after(carry, n, y, gain, eps, x, y2=ahead[0], h=ahead[1], alpha=following.alpha)
+                block.forward(x, ctx, cache, state, primed=primed, finish=finish)
+                primed = ahead
+                continue
+            block.forward(x, ctx, cache, state)
+            primed = None
             if self.stream:
                 self.stream.after(carry, n, x)
         if ctx.logits_rows.numel() == 0:

@@ -78,19 +78,32 @@ class PostNormBlock(Part):
             part.load(source)
         self.dtype = source.runtime.dtype
 
-    def forward(self, x, ctx, cache, state):
+    def readers(self, x):
+        """Buffers for what this block's first sublayer reads: (y, h) with y = alpha x and h = x in the compute dtype
+        (None in float32, where the sublayer reads x itself).  Whoever makes x may fill them (``primed``)."""
+        import torch
+        y = torch.empty_like(x)
+        h = torch.empty(x.shape, dtype=self.dtype, device=x.device) if self.dtype != torch.float32 else None
+        return y, h
+
+    def forward(self, x, ctx, cache, state, primed=None, finish=None):
+        """``primed``: (y, h) already filled for this x.  ``finish(y, gain, eps)``: instead of the block's last norm, the
+        caller's continuation, which must leave the layer's result (or what follows from it) in x."""
         import torch
         from .. import kernels
         narrow = self.dtype != torch.float32
-        y = torch.empty_like(x)
-        h = torch.empty(x.shape, dtype=self.dtype, device=x.device) if narrow else None
-        kernels.scale_cast(x, y, h, self.alpha)
+        if primed is None:
+            y, h = self.readers(x)
+            kernels.scale_cast(x, y, h, self.alpha)
+        else:
+            y, h = primed
         self.mixer.forward(h if narrow else x, y, ctx, cache, state)
         norm = self.norms[0]
-        if not self.has_ffn:
+        if self.has_ffn:
+            kernels.sum_norm(y, norm.gain, x, norm.eps, y2=y, h=h, alpha=self.alpha)
+            self.feed_forward.forward(h if narrow else x, y, ctx)
+            norm = self.norms[1]
+        if finish is not None:
+            finish(y, norm.gain, norm.eps)
+        else:
             kernels.sum_norm(y, norm.gain, x, norm.eps)
-            return
-        kernels.sum_norm(y, norm.gain, x, norm.eps, y2=y, h=h, alpha=self.alpha)
-        self.feed_forward.forward(h if narrow else x, y, ctx)
-        norm = self.norms[1]
-        kernels.sum_norm(y, norm.gain, x, norm.eps)

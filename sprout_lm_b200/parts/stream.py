@@ -35,3 +35,8 @@ class DepthWeightedAverage(Part):
 
     def after(self, history, n: int, x: torch.Tensor) -> None:
         kernels.depth_average(history, x, self.weights[n], n)
+
+    def norm_after(self, history, n: int, y, gain, eps: float, x, y2=None, h=None, alpha: float = 1.0) -> None:
+        """``after`` for a layer that ends in an RMS norm of ``y``: the norm, the average into ``x`` and, when given, the
+        next layer's readers ``y2 = alpha x`` and ``h`` (x in h's dtype) in one launch."""
+        kernels.sum_norm(y, gain, x, eps, y2=y2, h=h, alpha=alpha, history=history, weights=self.weights[n], n=n)

@@ -72,6 +72,20 @@ def test_depth_average_and_softcap():
         want = sum(float(weights[n][j]) * results[j].astype(np.float64) for j in range(n + 2))
         assert np.abs(x.cpu().numpy() - want).max() <= 1e-5
         assert torch.equal(history[n + 1].cpu(), torch.from_numpy(results[n + 1]))    # the result itself is kept, not the average
+    # the norm, the average and the next layer's readers in one launch give what the three steps give
+    for width in (12, 10):                     # rows that allow 16-byte accesses, and rows that do not
+        y = torch.from_numpy(rng.normal(0, 2, size=(4, width)).astype(np.float32)).to(DEV)
+        gain = torch.from_numpy(rng.normal(1, 0.2, size=width).astype(np.float32)).to(DEV)
+        w = torch.from_numpy(rng.normal(size=4).astype(np.float32)).to(DEV)
+        base = torch.from_numpy(rng.normal(size=(4, 4, width)).astype(np.float32)).to(DEV)
+        one, two = base.clone(), base.clone()
+        x1, y1, h1 = torch.empty_like(y), torch.empty_like(y), torch.empty(4, width, dtype=torch.bfloat16, device=DEV)
+        kernels.sum_norm(y, gain, x1, 1e-5, y2=y1, h=h1, alpha=1.5, history=one, weights=w, n=2)
+        x2, y2, h2 = torch.empty_like(y), torch.empty_like(y), torch.empty(4, width, dtype=torch.bfloat16, device=DEV)
+        kernels.sum_norm(y, gain, x2, 1e-5)
+        kernels.depth_average(two, x2, w, 2)
+        kernels.scale_cast(x2, y2, h2, 1.5)
+        assert torch.equal(one, two) and torch.equal(x1, x2) and torch.equal(y1, y2) and torch.equal(h1, h2)
     logits = torch.from_numpy(rng.normal(0, 20, size=(3, 17)).astype(np.float32)).to(DEV)
     want = plain.softcap(logits.double().cpu().numpy(), 7.5)
     kernels.softcap(logits, 7.5)
@@ -279,8 +293,10 @@ def test_layers_one_by_one(model_dirs):
         runner = make_runner(directory, "float32", 8, th.CONFIGS[name][2])
         seen = []
         stream = runner.model.stream
-        original = stream.after
+        original, original_fused = stream.after, stream.norm_after
         stream.after = lambda carry, n, x: (original(carry, n, x), seen.append(x.clone()))
+        stream.norm_after = lambda carry, n, y, gain, eps, x, **more: (original_fused(carry, n, y, gain, eps, x, **more),
+                                                                         seen.append(x.clone()))
         seq = runner.new_sequence()
         assert runner.reserve(seq, len(tokens))
         runner.step([StepEntry(seq, tokens, [0])])
