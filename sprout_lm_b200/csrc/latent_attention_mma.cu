@@ -347,29 +347,30 @@ latent_attention_rows_kernel(const LatentParams p) {
 }
 
 // ------------------------------------------------------------------------------ split keys (one token per request)
-template <int DVC, int CHUNKS>
-__global__ void __launch_bounds__(CHUNKS * 128)
+// PARTS warps per block of value columns take 16 keys of a stage each (KEYS = 16 PARTS); NSTAGES buffers, of which
+// NSTAGES - 1 are on their way while one is worked on.
+template <int DVC, int CHUNKS, int PARTS, int NSTAGES>
+__global__ void __launch_bounds__(CHUNKS * PARTS * 32)
 latent_attention_split_kernel(const LatentParams p) {
-  constexpr int KEYS = 64, THREADS = CHUNKS * 128;
+  constexpr int KEYS = 16 * PARTS, THREADS = CHUNKS * PARTS * 32;
   extern __shared__ __align__(16) uint8_t lsm[];
   const int stride = p.width + 8;
   __nv_bfloat16* sQ = (__nv_bfloat16*)lsm;            // [16][stride]
-  __nv_bfloat16* sK = sQ + 16 * stride;               // [2][KEYS][stride]; after the loop: the warps' partial sums
-  __shared__ __align__(8) uint64_t s_bar[2];
+  __nv_bfloat16* sK = sQ + 16 * stride;               // [NSTAGES][KEYS][stride]; after the loop: the warps' partial sums
+  __shared__ __align__(8) uint64_t s_bar[NSTAGES];
   __shared__ int s_failed;
-  __shared__ float s_ml[4][16][2];
-  __shared__ __align__(16) float s_part[CHUNKS * 4][256];   // a warp's partial scores, for the warp that shares its keys
+  __shared__ float s_ml[PARTS][16][2];
+  __shared__ __align__(16) float s_part[CHUNKS * PARTS][256];   // a warp's partial scores, for the warp that shares its keys
 
   pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid == 0) {
     s_failed = 0;
-    mbar_init(&s_bar[0], KEYS);
-    mbar_init(&s_bar[1], KEYS);
+    for (int i = 0; i < NSTAGES; i++) mbar_init(&s_bar[i], KEYS);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   pdl_wait();
-  const int quarter = warp & 3, chunk = warp >> 2;    // which 16 keys of a stage, which block of value columns
+  const int quarter = warp % PARTS, chunk = warp / PARTS;    // which 16 keys of a stage, which block of value columns
   const int groups = (p.heads + 15) / 16;
   const int r = blockIdx.x / groups, head0 = (blockIdx.x % groups) * 16;
   const int cta_col0 = blockIdx.y * CHUNKS * DVC, cta_col_end = min(p.rank, cta_col0 + CHUNKS * DVC);
@@ -388,7 +389,8 @@ latent_attention_split_kernel(const LatentParams p) {
   });
   cp_async_commit();
   __syncthreads();                                    // the mbarriers are initialised
-  if (stages > 0) issue_stage<KEYS>(p, table, first, last, sK, stride, &s_bar[0], tid);
+  for (int t = 0; t < NSTAGES - 1 && t < stages; t++)
+    issue_stage<KEYS>(p, table, first + t * KEYS, last, sK + t * KEYS * stride, stride, &s_bar[t], tid);
   cp_async_wait<0>();
 
   const int gr = lane >> 2, qc = lane & 3;
@@ -400,12 +402,15 @@ latent_attention_split_kernel(const LatentParams p) {
 #pragma unroll
   for (int i = 0; i < DVC / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   for (int t = 0; t < stages; t++) {
-    const int buf = t & 1;
-    __syncthreads();                                  // every warp is done with the other buffer; cleared rows are visible
+    const int buf = t % NSTAGES;
+    __syncthreads();                                  // every warp is done with the buffer before this one; cleared rows are visible
     if (s_failed) break;
-    if (t + 1 < stages) issue_stage<KEYS>(p, table, first + (t + 1) * KEYS, last, sK + (buf ^ 1) * KEYS * stride, stride, &s_bar[buf ^ 1], tid);
-    stage_landed(&s_bar[buf], (t >> 1) & 1, p.status, &s_failed);
-    const int key0 = first + t * KEYS + quarter * 16; // this warp's quarter of the stage
+    if (t + NSTAGES - 1 < stages) {
+      const int ahead = (t + NSTAGES - 1) % NSTAGES;  // the buffer that was worked on last
+      issue_stage<KEYS>(p, table, first + (t + NSTAGES - 1) * KEYS, last, sK + ahead * KEYS * stride, stride, &s_bar[ahead], tid);
+    }
+    stage_landed(&s_bar[buf], (t / NSTAGES) & 1, p.status, &s_failed);
+    const int key0 = first + t * KEYS + quarter * 16; // this warp's share of the stage
     if (key0 <= last && col0 < p.rank) {
       const __nv_bfloat16* tK = sK + (buf * KEYS + quarter * 16) * stride;
       float sc[2][4];
@@ -418,7 +423,7 @@ latent_attention_split_kernel(const LatentParams p) {
         mine[lane] = make_float4(sc[0][0], sc[0][1], sc[0][2], sc[0][3]);
         mine[32 + lane] = make_float4(sc[1][0], sc[1][1], sc[1][2], sc[1][3]);
         asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
-        const float4* other = (const float4*)s_part[warp ^ 4];
+        const float4* other = (const float4*)s_part[(warp + PARTS) % (2 * PARTS)];
         const float4 u = other[lane], v = other[32 + lane];
         sc[0][0] += u.x; sc[0][1] += u.y; sc[0][2] += u.z; sc[0][3] += u.w;
         sc[1][0] += v.x; sc[1][1] += v.y; sc[1][2] += v.z; sc[1][3] += v.w;
@@ -432,7 +437,7 @@ latent_attention_split_kernel(const LatentParams p) {
   __syncthreads();                                    // every warp is done with the stages: they become the exchange area
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-  float* so = (float*)sK;                             // [CHUNKS][4 quarters][16 rows][DVC]
+  float* so = (float*)sK;                             // [CHUNKS][PARTS][16 rows][DVC]
   if (qc == 0 && chunk == 0) {                        // every block of columns saw the same scores
     s_ml[quarter][gr][0] = m0 == -INFINITY ? -INFINITY : m0 * p.scale; s_ml[quarter][gr][1] = l0;
     s_ml[quarter][gr + 8][0] = m1 == -INFINITY ? -INFINITY : m1 * p.scale; s_ml[quarter][gr + 8][1] = l1;
@@ -449,12 +454,12 @@ latent_attention_split_kernel(const LatentParams p) {
     if (head0 + row >= p.heads) continue;
     float top = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 4; w++) top = fmaxf(top, s_ml[w][row][0]);
+    for (int w = 0; w < PARTS; w++) top = fmaxf(top, s_ml[w][row][0]);
     float sum = 0.f, l = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; w++) {
+    for (int w = 0; w < PARTS; w++) {
       const float f = s_ml[w][row][0] == -INFINITY ? 0.f : expf(s_ml[w][row][0] - top);
-      sum = fmaf(f, so[(((c / DVC) * 4 + w) * 16 + row) * DVC + c % DVC], sum);
+      sum = fmaf(f, so[(((c / DVC) * PARTS + w) * 16 + row) * DVC + c % DVC], sum);
       l = fmaf(f, s_ml[w][row][1], l);
     }
     const size_t at = ((size_t)r * p.splits + split) * p.heads + head0 + row;
@@ -538,7 +543,7 @@ SPROUT_API int sprout_latent_attention_mma_supported(int width, int rank) {
 }
 
 // splits == 0: whole rows (any mix of portions and single tokens).  splits >= 1: every request brings one token
-// and its keys are divided into `splits` ranges of `split_keys` (a multiple of 64) keys; `scratch` then holds
+// and its keys are divided into `splits` ranges of `split_keys` keys (a multiple of 64 fills whole stages); `scratch` then holds
 // requests * splits * heads * (rank + 2) floats.
 SPROUT_API int sprout_latent_attention_mma(const void* q, const void* cache, const int* block_table, int table_stride,
                                            const int* q_start, const int* positions, const int* context_lens,
@@ -580,21 +585,24 @@ SPROUT_API int sprout_latent_attention_mma(const void* q, const void* cache, con
     return sprout_check_launch("latent_attention_rows");
   }
   SPROUT_REQUIRE(splits <= 64, "latent_attention_mma: at most 64 ranges of keys (got %d)", splits);
-  SPROUT_REQUIRE(tokens == requests && context_lens && scratch && split_keys > 0 && split_keys % 64 == 0,
-                 "latent_attention_mma: split keys need one token per request, context lengths, scratch and ranges of a multiple of 64 keys");
-  // the stages' room is used again for the warps' partial sums: [chunks][4][16][DVC] floats
+  SPROUT_REQUIRE(tokens == requests && context_lens && scratch && split_keys > 0,
+                 "latent_attention_mma: split keys need one token per request, context lengths, scratch and a positive number of keys per range");
+  // Two stages of 64 keys, four warps per block of value columns.  (Measured against it: three stages, of 64 keys or for
+  // wide rows of 48 keys with three warps per block, were slower, 91 against 71 us at 64 requests of 2,048 keys and rows
+  // of 576: the kernel follows its warps' instruction chains, and the larger CTAs leave an SM fewer warps.)  The
+  // stages' room is used again for the warps' partial sums: [chunks][4][16][DVC] floats.
   const size_t exchange = (size_t)d.chunks * 4 * 16 * d.dvc * sizeof(float);
   const size_t smem = 16 * row_bytes + (2 * 64 * row_bytes > exchange ? 2 * 64 * row_bytes : exchange);
   SPROUT_REQUIRE(smem <= SPLIT_LIMIT, "latent_attention_mma: rows too wide for the split kernel's shared memory");
   dim3 grid(requests * ((heads + 15) / 16), d.ctas, splits);
-#define LAUNCH_SPLIT(DVC, CHUNKS)                                                                                   \
-  do {                                                                                                              \
-    if (prepare(latent_attention_split_kernel<DVC, CHUNKS>, smem)) return 1;                                              \
-    sprout_launch(latent_attention_split_kernel<DVC, CHUNKS>, grid, dim3(CHUNKS * 128), smem, stream, p);           \
+#define LAUNCH_SPLIT(DVC, CHUNKS, PARTS, NSTAGES)                                                                          \
+  do {                                                                                                                     \
+    if (prepare(latent_attention_split_kernel<DVC, CHUNKS, PARTS, NSTAGES>, smem)) return 1;                               \
+    sprout_launch(latent_attention_split_kernel<DVC, CHUNKS, PARTS, NSTAGES>, grid, dim3(CHUNKS * PARTS * 32), smem, stream, p); \
   } while (0)
-  if (d.dvc == 128) LAUNCH_SPLIT(128, 1);
-  else if (d.chunks == 1) LAUNCH_SPLIT(256, 1);
-  else LAUNCH_SPLIT(256, 2);
+  if (d.dvc == 128) LAUNCH_SPLIT(128, 1, 4, 2);
+  else if (d.chunks == 1) LAUNCH_SPLIT(256, 1, 4, 2);
+  else LAUNCH_SPLIT(256, 2, 4, 2);
 #undef LAUNCH_SPLIT
   if (int code = sprout_check_launch("latent_attention_split")) return code;
   sprout_launch(latent_attention_merge_kernel, dim3(requests, heads), dim3(128), 0, stream, p);

@@ -996,12 +996,12 @@ def latent_split_plan(requests: int, heads: int, rank: int, planned_keys: int, w
     row_bytes = (max(width, rank) + 8) * 2
     blocks = 1 if rank <= 256 else 2
     shared = 16 * row_bytes + max(128 * row_bytes, blocks * 4 * 16 * (128 if rank <= 128 else 256) * 4)
-    per_sm = max(1, min(4, 227 * 1024 // (shared + 2048)))
+    per_sm = max(1, min(4, 232448 // (shared + 10240)))
     stages = max(1, -(-planned_keys // 64))
     # a range is worth its fixed costs (query rows, exchange, partial sums through memory) from four stages on
     splits = max(1, min(per_sm * sm_count() // max(1, requests * groups * along_y), stages // 4, 64))
     split_keys = -(-stages // splits) * 64
-    return -(-stages * 64 // split_keys), split_keys
+    return max(1, -(-planned_keys // split_keys)), split_keys
 
 
 def latent_attention_mma(qlat, cache, block_table, q_start, positions, context_lens, sink, out, heads: int, rank: int,
