@@ -176,14 +176,20 @@ __device__ __forceinline__ void bulk_row(void* dst, const void* src, uint32_t by
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
+// The page of a thread's key row in a stage (read one stage ahead of its use, so that the load's latency is not on the
+// stage's path): -2 for a key beyond the range, else the block table's entry.
 template <int KEYS>
-__device__ __forceinline__ void issue_stage(const LatentParams& p, const int* table, int first_key, int last_key,
-                                            __nv_bfloat16* dst, int stride, uint64_t* bar, int tid) {
+__device__ __forceinline__ int page_ahead(const LatentParams& p, const int* table, int first_key, int last_key, int tid) {
+  const int key = first_key + tid;
+  return (tid < KEYS && key <= last_key) ? table[key / p.page_tokens] : -2;
+}
+template <int KEYS>
+__device__ __forceinline__ void issue_stage(const LatentParams& p, int page, int first_key, __nv_bfloat16* dst, int stride,
+                                            uint64_t* bar, int tid) {
   if (tid < KEYS) {
     const int key = first_key + tid;
     long long off = -1;
-    if (key <= last_key) {
-      const int page = table[key / p.page_tokens];
+    if (page != -2) {
       if (page < 0 || page >= p.num_pages) atomicOr(p.status, SPROUT_STATUS_BAD_PAGE);
       else off = ((long long)page * p.page_tokens + key % p.page_tokens) * p.width;
     }
@@ -276,7 +282,8 @@ latent_attention_rows_kernel(const LatentParams p) {
     else *(uint4*)dst = make_uint4(0, 0, 0, 0);
   });
   cp_async_commit();
-  issue_stage<KEYS>(p, table, 0, max_limit, sK, stride, &s_bar[0], tid);
+  issue_stage<KEYS>(p, page_ahead<KEYS>(p, table, 0, max_limit, tid), 0, sK, stride, &s_bar[0], tid);
+  int page_next = page_ahead<KEYS>(p, table, KEYS, max_limit, tid);       // of the stage after: read now, used at the loop's next turn
   cp_async_wait<0>();                                 // this thread's pieces of the query rows; the loop's first barrier publishes them
 
   const int gr = lane >> 2, qc = lane & 3;
@@ -301,7 +308,10 @@ latent_attention_rows_kernel(const LatentParams p) {
     const int buf = t & 1;
     __syncthreads();                                  // every warp is done with the other buffer; cleared rows are visible
     if (s_failed) break;
-    if (t + 1 < stages) issue_stage<KEYS>(p, table, (t + 1) * KEYS, max_limit, sK + (buf ^ 1) * KEYS * stride, stride, &s_bar[buf ^ 1], tid);
+    if (t + 1 < stages) {
+      issue_stage<KEYS>(p, page_next, (t + 1) * KEYS, sK + (buf ^ 1) * KEYS * stride, stride, &s_bar[buf ^ 1], tid);
+      page_next = page_ahead<KEYS>(p, table, (t + 2) * KEYS, max_limit, tid);
+    }
     stage_landed(&s_bar[buf], (t >> 1) & 1, p.status, &s_failed);
     const int key0 = t * KEYS;
     if (active && key0 <= warp_limit) {
@@ -350,7 +360,7 @@ latent_attention_rows_kernel(const LatentParams p) {
 // PARTS warps per block of value columns take 16 keys of a stage each (KEYS = 16 PARTS); NSTAGES buffers, of which
 // NSTAGES - 1 are on their way while one is worked on.
 template <int DVC, int CHUNKS, int PARTS, int NSTAGES>
-__global__ void __launch_bounds__(CHUNKS * PARTS * 32)
+__global__ void __launch_bounds__(CHUNKS * PARTS * 32, 4 / CHUNKS)        // 128 registers a thread: 16 warps on an SM
 latent_attention_split_kernel(const LatentParams p) {
   constexpr int KEYS = 16 * PARTS, THREADS = CHUNKS * PARTS * 32;
   extern __shared__ __align__(16) uint8_t lsm[];
@@ -390,13 +400,15 @@ latent_attention_split_kernel(const LatentParams p) {
   cp_async_commit();
   __syncthreads();                                    // the mbarriers are initialised
   for (int t = 0; t < NSTAGES - 1 && t < stages; t++)
-    issue_stage<KEYS>(p, table, first + t * KEYS, last, sK + t * KEYS * stride, stride, &s_bar[t], tid);
+    issue_stage<KEYS>(p, page_ahead<KEYS>(p, table, first + t * KEYS, last, tid), first + t * KEYS, sK + t * KEYS * stride, stride,
+                      &s_bar[t], tid);
+  int page_next = page_ahead<KEYS>(p, table, first + (NSTAGES - 1) * KEYS, last, tid);   // read now, used at the loop's next turn
   cp_async_wait<0>();
 
   const int gr = lane >> 2, qc = lane & 3;
   const float scale_log2 = p.scale * 1.4426950408889634f;
   const int steps = p.width / 16;
-  const bool paired = CHUNKS == 2 && cta_col0 + DVC < p.rank;          // both blocks of value columns exist
+  const bool shared_scores = CHUNKS > 1 && cta_col0 + (CHUNKS - 1) * DVC < p.rank;      // all the CTA's blocks of value columns exist
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
   float o[DVC / 8][4];
 #pragma unroll
@@ -407,26 +419,33 @@ latent_attention_split_kernel(const LatentParams p) {
     if (s_failed) break;
     if (t + NSTAGES - 1 < stages) {
       const int ahead = (t + NSTAGES - 1) % NSTAGES;  // the buffer that was worked on last
-      issue_stage<KEYS>(p, table, first + (t + NSTAGES - 1) * KEYS, last, sK + ahead * KEYS * stride, stride, &s_bar[ahead], tid);
+      issue_stage<KEYS>(p, page_next, first + (t + NSTAGES - 1) * KEYS, sK + ahead * KEYS * stride, stride, &s_bar[ahead], tid);
+      page_next = page_ahead<KEYS>(p, table, first + (t + NSTAGES) * KEYS, last, tid);
     }
     stage_landed(&s_bar[buf], (t / NSTAGES) & 1, p.status, &s_failed);
     const int key0 = first + t * KEYS + quarter * 16; // this warp's share of the stage
     if (key0 <= last && col0 < p.rank) {
       const __nv_bfloat16* tK = sK + (buf * KEYS + quarter * 16) * stride;
       float sc[2][4];
-      if (paired) {
-        // the two warps that hold the same keys (one per block of value columns) take half of the rows' width each
-        // and add their partial scores through shared memory
-        const int half = (steps + 1) / 2;
-        scores_block<2>(sQ, tK, stride, chunk ? half : 0, chunk ? steps : half, sc, lane);
+      if (shared_scores) {
+        // the warps that hold the same keys (one per block of value columns) take a share of the rows' width each and add
+        // their partial scores through shared memory
+        const int k0 = steps * chunk / CHUNKS, k1 = steps * (chunk + 1) / CHUNKS;
+        scores_block<2>(sQ, tK, stride, k0, k1, sc, lane);
         float4* mine = (float4*)s_part[warp];
         mine[lane] = make_float4(sc[0][0], sc[0][1], sc[0][2], sc[0][3]);
         mine[32 + lane] = make_float4(sc[1][0], sc[1][1], sc[1][2], sc[1][3]);
-        asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
-        const float4* other = (const float4*)s_part[(warp + PARTS) % (2 * PARTS)];
-        const float4 u = other[lane], v = other[32 + lane];
-        sc[0][0] += u.x; sc[0][1] += u.y; sc[0][2] += u.z; sc[0][3] += u.w;
-        sc[1][0] += v.x; sc[1][1] += v.y; sc[1][2] += v.z; sc[1][3] += v.w;
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + quarter), "r"(CHUNKS * 32) : "memory");
+        // every warp adds the shares in the same order, its own among them: all of them hold the same scores, bit for bit
+#pragma unroll
+        for (int j = 0; j < 4; j++) sc[0][j] = sc[1][j] = 0.f;
+#pragma unroll
+        for (int from = 0; from < CHUNKS; from++) {
+          const float4* share = (const float4*)s_part[from * PARTS + quarter];
+          const float4 u = share[lane], v = share[32 + lane];
+          sc[0][0] += u.x; sc[0][1] += u.y; sc[0][2] += u.z; sc[0][3] += u.w;
+          sc[1][0] += v.x; sc[1][1] += v.y; sc[1][2] += v.z; sc[1][3] += v.w;
+        }
       } else {
         scores_block<2>(sQ, tK, stride, 0, steps, sc, lane);
       }
@@ -503,7 +522,7 @@ latent_attention_merge_kernel(const LatentParams p) {
 }
 
 // dynamic bytes a CTA may ask for beside the kernels' static arrays (the split kernel's hold the warps' partial scores)
-constexpr size_t ROWS_LIMIT = 232448 - 2048, SPLIT_LIMIT = 232448 - 10240;
+constexpr size_t ROWS_LIMIT = 232448 - 2048, SPLIT_LIMIT = 232448 - 18432;
 
 // Raise a kernel's dynamic shared memory limit to what the SM has left beside the kernel's static arrays (once per
 // kernel), and refuse a launch that wants more.
@@ -530,6 +549,12 @@ inline Division divide(int rank) {
   if (rank <= 128) return {128, 1, 1};
   if (rank <= 256) return {256, 1, 1};
   return {256, 2, (rank + 511) / 512};
+}
+// The split-key kernel takes blocks of 128 columns (half the accumulator registers, twice the warps an SM holds).
+inline Division divide_split(int rank) {
+  if (rank <= 128) return {128, 1, 1};
+  if (rank <= 256) return {128, 2, 1};
+  return {128, 4, (rank + 511) / 512};
 }
 
 }  // namespace
@@ -587,22 +612,23 @@ SPROUT_API int sprout_latent_attention_mma(const void* q, const void* cache, con
   SPROUT_REQUIRE(splits <= 64, "latent_attention_mma: at most 64 ranges of keys (got %d)", splits);
   SPROUT_REQUIRE(tokens == requests && context_lens && scratch && split_keys > 0,
                  "latent_attention_mma: split keys need one token per request, context lengths, scratch and a positive number of keys per range");
-  // Two stages of 64 keys, four warps per block of value columns.  (Measured against it: three stages, of 64 keys or for
-  // wide rows of 48 keys with three warps per block, were slower, 91 against 71 us at 64 requests of 2,048 keys and rows
-  // of 576: the kernel follows its warps' instruction chains, and the larger CTAs leave an SM fewer warps.)  The
-  // stages' room is used again for the warps' partial sums: [chunks][4][16][DVC] floats.
-  const size_t exchange = (size_t)d.chunks * 4 * 16 * d.dvc * sizeof(float);
+  // Two stages of 64 keys, four warps per block of 128 value columns, up to four blocks (16 warps) per CTA.  (Measured
+  // against it: three stages, of 64 keys or for wide rows of 48 keys with three warps per block, were slower, 91 against
+  // 71 us at 64 requests of 2,048 keys and rows of 576: the kernel follows its warps' instruction chains, and larger CTAs
+  // leave an SM fewer warps.)  The stages' room is used again for the warps' partial sums: [chunks][4][16][128] floats.
+  const Division ds = divide_split(rank);
+  const size_t exchange = (size_t)ds.chunks * 4 * 16 * ds.dvc * sizeof(float);
   const size_t smem = 16 * row_bytes + (2 * 64 * row_bytes > exchange ? 2 * 64 * row_bytes : exchange);
   SPROUT_REQUIRE(smem <= SPLIT_LIMIT, "latent_attention_mma: rows too wide for the split kernel's shared memory");
-  dim3 grid(requests * ((heads + 15) / 16), d.ctas, splits);
+  dim3 grid(requests * ((heads + 15) / 16), ds.ctas, splits);
 #define LAUNCH_SPLIT(DVC, CHUNKS, PARTS, NSTAGES)                                                                          \
   do {                                                                                                                     \
     if (prepare(latent_attention_split_kernel<DVC, CHUNKS, PARTS, NSTAGES>, smem)) return 1;                               \
     sprout_launch(latent_attention_split_kernel<DVC, CHUNKS, PARTS, NSTAGES>, grid, dim3(CHUNKS * PARTS * 32), smem, stream, p); \
   } while (0)
-  if (d.dvc == 128) LAUNCH_SPLIT(128, 1, 4, 2);
-  else if (d.chunks == 1) LAUNCH_SPLIT(256, 1, 4, 2);
-  else LAUNCH_SPLIT(256, 2, 4, 2);
+  if (ds.chunks == 1) LAUNCH_SPLIT(128, 1, 4, 2);
+  else if (ds.chunks == 2) LAUNCH_SPLIT(128, 2, 4, 2);
+  else LAUNCH_SPLIT(128, 4, 4, 2);
 #undef LAUNCH_SPLIT
   if (int code = sprout_check_launch("latent_attention_split")) return code;
   sprout_launch(latent_attention_merge_kernel, dim3(requests, heads), dim3(128), 0, stream, p);

@@ -994,9 +994,9 @@ def latent_split_plan(requests: int, heads: int, rank: int, planned_keys: int, w
     plan alike."""
     groups, along_y = -(-heads // 16), 1 if rank <= 512 else -(-rank // 512)
     row_bytes = (max(width, rank) + 8) * 2
-    blocks = 1 if rank <= 256 else 2
-    shared = 16 * row_bytes + max(128 * row_bytes, blocks * 4 * 16 * (128 if rank <= 128 else 256) * 4)
-    per_sm = max(1, min(4, 232448 // (shared + 10240)))
+    blocks = 1 if rank <= 128 else 2 if rank <= 256 else 4             # of 128 value columns, four warps each
+    shared = 16 * row_bytes + max(128 * row_bytes, blocks * 4 * 16 * 128 * 4)
+    per_sm = max(1, min(4 // blocks, 232448 // (shared + 18432)))       # by registers (128 a thread) and by shared memory
     stages = max(1, -(-planned_keys // 64))
     # a range is worth its fixed costs (query rows, exchange, partial sums through memory) from four stages on
     splits = max(1, min(per_sm * sm_count() // max(1, requests * groups * along_y), stages // 4, 64))
