@@ -1,0 +1,199 @@
+// Row kernels of layers that wrap every sublayer in two norms, all float32 arithmetic:
+//  * layernorm:      out = (x - mean) / sqrt(var + eps) * w, var the mean of the squared deviations
+//                    (no bias); rows may be selected by index.
+//  * norm_add:       x += layernorm(y) * w_b, and, when asked, h = layernorm(x) * w_next of the new x:
+//                    the norm after a sublayer, the residual sum and the norm before the next
+//                    sublayer in one launch.
+//  * gated_rmsnorm:  out = o / sqrt(mean(o^2) + eps) * w * sigmoid(gate).
+//  * relu2, glu_clamped: activations between the two products of a feed-forward.
+// One block per row; sums in a fixed order that depends on the block size alone, so a row's result
+// does not depend on what else is in the batch.
+#include "common.cuh"
+
+namespace {
+
+constexpr int THREADS = 256;
+
+// mean and 1 / sqrt(var + eps) of a row held in shared memory (two passes: the deviations are exact)
+__device__ __forceinline__ void row_moments(const float* row, int width, float eps, float* scratch, float& mean, float& rstd) {
+  float s = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) s += row[i];
+  mean = block_sum(s, scratch) / (float)width;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float d = row[i] - mean;
+    q = fmaf(d, d, q);
+  }
+  rstd = 1.0f / sqrtf(block_sum(q, scratch) / (float)width + eps);
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(THREADS)
+layernorm_kernel(const float* __restrict__ x, const float* __restrict__ gain, TO* __restrict__ out,
+                 const int* __restrict__ rows, int width, float eps) {
+  extern __shared__ float smem[];
+  float* row = smem;                 // width
+  float* scratch = smem + width;     // 33
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t src = (size_t)(rows ? rows[blockIdx.x] : blockIdx.x) * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = x[src + i];
+  __syncthreads();
+  float mean, rstd;
+  row_moments(row, width, eps, scratch, mean, rstd);
+  TO* dst = out + (size_t)blockIdx.x * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_float<TO>((row[i] - mean) * rstd * gain[i]);
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(THREADS)
+norm_add_kernel(const float* __restrict__ y, const float* __restrict__ gain, float* __restrict__ x,
+                const float* __restrict__ next_gain, TO* __restrict__ h, int width, float eps) {
+  extern __shared__ float smem[];
+  float* row = smem;
+  float* scratch = smem + width;
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t at = (size_t)blockIdx.x * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = y[at + i];
+  __syncthreads();
+  float mean, rstd;
+  row_moments(row, width, eps, scratch, mean, rstd);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {      // each thread rewrites the elements it read
+    const float v = x[at + i] + (row[i] - mean) * rstd * gain[i];
+    x[at + i] = v;
+    row[i] = v;
+  }
+  if (next_gain == nullptr) return;
+  __syncthreads();
+  row_moments(row, width, eps, scratch, mean, rstd);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) h[at + i] = from_float<TO>((row[i] - mean) * rstd * next_gain[i]);
+}
+
+template <typename TG, typename TO>
+__global__ void __launch_bounds__(THREADS)
+gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ gain, const TG* __restrict__ gate,
+                     int gate_stride, TO* __restrict__ out, int width, float eps) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t at = (size_t)blockIdx.x * width;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = o[at + i];
+    q = fmaf(v, v, q);
+  }
+  const float r = 1.0f / sqrtf(block_sum(q, scratch) / (float)width + eps);
+  const TG* grow = gate + (size_t)blockIdx.x * gate_stride;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float g = to_float(grow[i]);
+    out[at + i] = from_float<TO>(o[at + i] * r * gain[i] * (1.0f / (1.0f + expf(-g))));
+  }
+}
+
+template <typename T>
+__global__ void relu2_kernel(const T* __restrict__ z, T* __restrict__ out, long long count) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
+    const float v = fmaxf(to_float(z[i]), 0.f);
+    out[i] = from_float<T>(v * v);
+  }
+}
+
+// rows of [gate (ff) | up (ff)] -> g * sigmoid(alpha g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit)
+template <typename T>
+__global__ void glu_clamped_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int ff, float limit, float alpha) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long count = (long long)rows * ff;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / ff;
+    const int j = (int)(i - r * ff);
+    const float g = fminf(to_float(gate_up[r * 2 * ff + j]), limit);
+    const float u = fminf(fmaxf(to_float(gate_up[r * 2 * ff + ff + j]), -limit), limit);
+    out[i] = from_float<T>(g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f));
+  }
+}
+
+int grid_for(long long count) { return (int)((count + 255) / 256 < 148 * 8 ? (count + 255) / 256 : 148 * 8); }
+
+}  // namespace
+
+SPROUT_API int sprout_layernorm(const float* x, const float* gain, void* out, int out_dtype, const int* rows, int count,
+                                int width, float eps, cudaStream_t stream) {
+  SPROUT_REQUIRE(x && gain && out && count > 0 && width > 0 && eps > 0, "layernorm: bad arguments");
+  SPROUT_REQUIRE(width <= 40000, "layernorm: rows of up to 40000 elements (got %d)", width);
+  const size_t smem = (size_t)(width + 34) * sizeof(float);
+  if (out_dtype == SPROUT_F32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sprout_launch(layernorm_kernel<float>, dim3(count), dim3(THREADS), smem, stream, x, gain, (float*)out, rows, width, eps);
+  } else if (out_dtype == SPROUT_BF16) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sprout_launch(layernorm_kernel<__nv_bfloat16>, dim3(count), dim3(THREADS), smem, stream, x, gain, (__nv_bfloat16*)out, rows, width, eps);
+  } else {
+    return sprout_fail("layernorm: unknown dtype %d", out_dtype);
+  }
+  return sprout_check_launch("layernorm");
+}
+
+// x [count, width] += layernorm(y) * gain; with next_gain also h = layernorm(x) * next_gain (h in h_dtype).
+SPROUT_API int sprout_norm_add(const float* y, const float* gain, float* x, const float* next_gain, void* h, int h_dtype,
+                               int count, int width, float eps, cudaStream_t stream) {
+  SPROUT_REQUIRE(y && gain && x && count > 0 && width > 0 && eps > 0, "norm_add: bad arguments");
+  SPROUT_REQUIRE((next_gain == nullptr) == (h == nullptr), "norm_add: the next norm's gain and its output go together");
+  SPROUT_REQUIRE(width <= 40000, "norm_add: rows of up to 40000 elements (got %d)", width);
+  const size_t smem = (size_t)(width + 34) * sizeof(float);
+  if (h_dtype == SPROUT_F32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(norm_add_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sprout_launch(norm_add_kernel<float>, dim3(count), dim3(THREADS), smem, stream, y, gain, x, next_gain, (float*)h, width, eps);
+  } else if (h_dtype == SPROUT_BF16) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(norm_add_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sprout_launch(norm_add_kernel<__nv_bfloat16>, dim3(count), dim3(THREADS), smem, stream, y, gain, x, next_gain, (__nv_bfloat16*)h, width, eps);
+  } else {
+    return sprout_fail("norm_add: unknown dtype %d", h_dtype);
+  }
+  return sprout_check_launch("norm_add");
+}
+
+// out [count, width] = o / rms(o) * gain * sigmoid(gate); gate rows have stride gate_stride and out's dtype.
+SPROUT_API int sprout_gated_rmsnorm(const float* o, const float* gain, const void* gate, int gate_stride, void* out, int dtype,
+                                    int count, int width, float eps, cudaStream_t stream) {
+  SPROUT_REQUIRE(o && gain && gate && out && count > 0 && width > 0 && eps > 0 && gate_stride >= width, "gated_rmsnorm: bad arguments");
+  if (dtype == SPROUT_F32)
+    sprout_launch(gated_rmsnorm_kernel<float, float>, dim3(count), dim3(THREADS), 0, stream, o, gain, (const float*)gate,
+                  gate_stride, (float*)out, width, eps);
+  else if (dtype == SPROUT_BF16)
+    sprout_launch(gated_rmsnorm_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(count), dim3(THREADS), 0, stream, o, gain,
+                  (const __nv_bfloat16*)gate, gate_stride, (__nv_bfloat16*)out, width, eps);
+  else
+    return sprout_fail("gated_rmsnorm: unknown dtype %d", dtype);
+  return sprout_check_launch("gated_rmsnorm");
+}
+
+SPROUT_API int sprout_relu2(const void* z, void* out, int dtype, long long count, cudaStream_t stream) {
+  SPROUT_REQUIRE(z && out && count > 0, "relu2: bad arguments");
+  if (dtype == SPROUT_F32)
+    sprout_launch(relu2_kernel<float>, dim3(grid_for(count)), dim3(256), 0, stream, (const float*)z, (float*)out, count);
+  else if (dtype == SPROUT_BF16)
+    sprout_launch(relu2_kernel<__nv_bfloat16>, dim3(grid_for(count)), dim3(256), 0, stream, (const __nv_bfloat16*)z,
+                  (__nv_bfloat16*)out, count);
+  else
+    return sprout_fail("relu2: unknown dtype %d", dtype);
+  return sprout_check_launch("relu2");
+}
+
+SPROUT_API int sprout_glu_clamped(const void* gate_up, void* out, int dtype, int rows, int ff, float limit, float alpha,
+                                  cudaStream_t stream) {
+  SPROUT_REQUIRE(gate_up && out && rows > 0 && ff > 0 && limit > 0, "glu_clamped: bad arguments");
+  const long long count = (long long)rows * ff;
+  if (dtype == SPROUT_F32)
+    sprout_launch(glu_clamped_kernel<float>, dim3(grid_for(count)), dim3(256), 0, stream, (const float*)gate_up, (float*)out,
+                  rows, ff, limit, alpha);
+  else if (dtype == SPROUT_BF16)
+    sprout_launch(glu_clamped_kernel<__nv_bfloat16>, dim3(grid_for(count)), dim3(256), 0, stream,
+                  (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows, ff, limit, alpha);
+  else
+    return sprout_fail("glu_clamped: unknown dtype %d", dtype);
+  return sprout_check_launch("glu_clamped");
+}

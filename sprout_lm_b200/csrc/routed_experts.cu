@@ -1,0 +1,280 @@
+// A routed feed-forward (mixture of experts), all on the device: no count ever travels to the host.
+//
+//  * moe_route:    per token z = W_router h (float32), s = softmax(z) over all router outputs,
+//                  choice = s + correction; the `top` largest choices (lowest index first among equals) are
+//                  taken; weight = s / (sum of the taken s + 1e-20) * scale.  Router outputs from
+//                  `experts` on are identity experts (their output is the token's h).  Counts the rows
+//                  of each real expert.
+//  * moe_arrange:  offsets of the experts' row ranges, every taken (token, place) of a real expert put
+//                  into its expert's range (`sorted`), and where it went (`place_of`).
+//  * moe_up / moe_down (plain): the experts' two products on CUDA cores over the arranged rows, every
+//                  output element summed in ascending k by one warp: act = f(W_gate a, W_up a),
+//                  rows = W_down act, f(g, u) = g' sigmoid(alpha g') (u' + 1), g' = min(g, limit),
+//                  u' = clamp(u, -limit, limit).
+//  * moe_combine:  y[t] += sum over the token's places of weight * (identity ? h[t] : its row).
+#include "common.cuh"
+
+namespace {
+
+constexpr int ROUTE_WARPS = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_route_kernel(const T* __restrict__ h, int h_stride, const float* __restrict__ router, const float* __restrict__ correction,
+                 int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ counts, int tokens, int width,
+                 int outputs, int experts, int top, float scale) {
+  extern __shared__ float smem[];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * ROUTE_WARPS + warp;
+  if (t >= tokens) return;
+  float* z = smem + (size_t)warp * 2 * outputs;     // scores, then choices
+  float* choice = z + outputs;
+  const T* row = h + (size_t)t * h_stride;
+  for (int e = 0; e < outputs; e++) {
+    const float* w = router + (size_t)e * width;
+    float dot = 0.f;
+    for (int k = lane; k < width; k += 32) dot = fmaf(to_float(row[k]), w[k], dot);
+    dot = warp_sum(dot);
+    if (lane == 0) z[e] = dot;
+  }
+  __syncwarp();
+  float top_z = -INFINITY;
+  for (int e = lane; e < outputs; e += 32) top_z = fmaxf(top_z, z[e]);
+  top_z = warp_max(top_z);
+  float sum = 0.f;
+  for (int e = lane; e < outputs; e += 32) sum += expf(z[e] - top_z);
+  sum = warp_sum(sum);
+  __syncwarp();
+  for (int e = lane; e < outputs; e += 32) {
+    const float s = expf(z[e] - top_z) / sum;
+    z[e] = s;
+    choice[e] = s + correction[e];
+  }
+  __syncwarp();
+  if (lane == 0) {
+    float taken = 0.f;
+    for (int place = 0; place < top; place++) {
+      int best = -1;
+      float best_c = -INFINITY;
+      for (int e = 0; e < outputs; e++)
+        if (choice[e] > best_c) {
+          best_c = choice[e];
+          best = e;
+        }
+      if (best < 0) best = 0;          // non-finite scores: the status of the logits will tell
+      choice[best] = -INFINITY;
+      ids[(size_t)t * top + place] = best;
+      weights[(size_t)t * top + place] = z[best];
+      taken += z[best];
+      if (best < experts) atomicAdd(&counts[best], 1);
+    }
+    const float norm = scale / (taken + 1e-20f);
+    for (int place = 0; place < top; place++) weights[(size_t)t * top + place] *= norm;
+  }
+}
+
+// One block.  counts -> offsets [experts + 1]; counts are left zeroed for the next call.
+__global__ void __launch_bounds__(1024)
+moe_arrange_kernel(const int* __restrict__ ids, int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ sorted,
+                   int* __restrict__ place_of, int entries, int experts) {
+  extern __shared__ int cursor[];       // experts
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < experts; e++) {
+      offsets[e] = at;
+      cursor[e] = at;
+      at += counts[e];
+      counts[e] = 0;
+    }
+    offsets[experts] = at;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < entries; i += blockDim.x) {
+    const int e = ids[i];
+    if (e < experts) {
+      const int at = atomicAdd(&cursor[e], 1);
+      sorted[at] = i;
+      place_of[i] = at;
+    } else {
+      place_of[i] = -1;
+    }
+  }
+}
+
+__device__ __forceinline__ int expert_of(const int* offsets, int experts, int row) {
+  int lo = 0, hi = experts;            // the last e with offsets[e] <= row
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) / 2;
+    if (offsets[mid] <= row) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+__device__ __forceinline__ float glu(float g, float u, float limit, float alpha) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+}
+
+// grid (rows, column blocks); 8 warps, a warp per output column at a time.  w_gate_up [experts, 2 ff, width] with
+// gate rows first; act [rows, ff].
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_up_plain_kernel(const T* __restrict__ h, int h_stride, const int* __restrict__ sorted, const int* __restrict__ offsets,
+                    const T* __restrict__ w_gate_up, T* __restrict__ act, int experts, int top, int width, int ff,
+                    float limit, float alpha) {
+  extern __shared__ float a[];          // width
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x;
+  if (row >= offsets[experts]) return;
+  const int e = expert_of(offsets, experts, row);
+  const T* src = h + (size_t)(sorted[row] / top) * h_stride;
+  for (int k = threadIdx.x; k < width; k += blockDim.x) a[k] = to_float(src[k]);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const T* w = w_gate_up + (size_t)e * 2 * ff * width;
+  for (int j = blockIdx.y * 8 + warp; j < ff; j += gridDim.y * 8) {
+    const T* wg = w + (size_t)j * width;
+    const T* wu = w + (size_t)(ff + j) * width;
+    float g = 0.f, u = 0.f;
+    for (int k = lane; k < width; k += 32) {
+      g = fmaf(a[k], to_float(wg[k]), g);
+      u = fmaf(a[k], to_float(wu[k]), u);
+    }
+    g = warp_sum(g);
+    u = warp_sum(u);
+    // the products' results are rounded to the activations' type before the activation, as separate products would leave them
+    if (lane == 0) act[(size_t)row * ff + j] = from_float<T>(glu(to_float(from_float<T>(g)), to_float(from_float<T>(u)), limit, alpha));
+  }
+}
+
+// w_down [experts, width, ff]; rows_out float32 [rows, width].
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_down_plain_kernel(const T* __restrict__ act, const int* __restrict__ offsets, const T* __restrict__ w_down,
+                      float* __restrict__ rows_out, int experts, int width, int ff) {
+  extern __shared__ float a[];          // ff
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x;
+  if (row >= offsets[experts]) return;
+  const int e = expert_of(offsets, experts, row);
+  for (int k = threadIdx.x; k < ff; k += blockDim.x) a[k] = to_float(act[(size_t)row * ff + k]);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const T* w = w_down + (size_t)e * width * ff;
+  for (int n = blockIdx.y * 8 + warp; n < width; n += gridDim.y * 8) {
+    const T* wn = w + (size_t)n * ff;
+    float s = 0.f;
+    for (int k = lane; k < ff; k += 32) s = fmaf(a[k], to_float(wn[k]), s);
+    s = warp_sum(s);
+    if (lane == 0) rows_out[(size_t)row * width + n] = s;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(float* __restrict__ y, const T* __restrict__ h, int h_stride, const int* __restrict__ ids,
+                   const float* __restrict__ weights, const int* __restrict__ place_of, const float* __restrict__ rows,
+                   int width, int top) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  for (int n = threadIdx.x; n < width; n += blockDim.x) {
+    float sum = 0.f;
+    for (int place = 0; place < top; place++) {
+      const int at = place_of[(size_t)t * top + place];
+      const float w = weights[(size_t)t * top + place];
+      sum = fmaf(w, at < 0 ? to_float(h[(size_t)t * h_stride + n]) : rows[(size_t)at * width + n], sum);
+    }
+    y[(size_t)t * width + n] += sum;
+  }
+}
+
+}  // namespace
+
+SPROUT_API int sprout_moe_route(const void* h, int h_stride, int dtype, const float* router, const float* correction, int* ids,
+                                float* weights, int* counts, int tokens, int width, int outputs, int experts, int top,
+                                float scale, cudaStream_t stream) {
+  SPROUT_REQUIRE(h && router && correction && ids && weights && counts, "moe_route: null pointer");
+  SPROUT_REQUIRE(tokens > 0 && width > 0 && outputs > 0 && experts >= 0 && experts <= outputs && top > 0 && top <= outputs,
+                 "moe_route: bad sizes (outputs %d, experts %d, top %d)", outputs, experts, top);
+  const size_t smem = (size_t)ROUTE_WARPS * 2 * outputs * sizeof(float);
+  SPROUT_REQUIRE(smem <= 48 * 1024, "moe_route: too many router outputs (%d)", outputs);
+  dim3 grid((tokens + ROUTE_WARPS - 1) / ROUTE_WARPS);
+  if (dtype == SPROUT_F32)
+    sprout_launch(moe_route_kernel<float>, grid, dim3(ROUTE_WARPS * 32), smem, stream, (const float*)h, h_stride, router,
+                  correction, ids, weights, counts, tokens, width, outputs, experts, top, scale);
+  else if (dtype == SPROUT_BF16)
+    sprout_launch(moe_route_kernel<__nv_bfloat16>, grid, dim3(ROUTE_WARPS * 32), smem, stream, (const __nv_bfloat16*)h, h_stride,
+                  router, correction, ids, weights, counts, tokens, width, outputs, experts, top, scale);
+  else
+    return sprout_fail("moe_route: unknown dtype %d", dtype);
+  return sprout_check_launch("moe_route");
+}
+
+SPROUT_API int sprout_moe_arrange(const int* ids, int* counts, int* offsets, int* sorted, int* place_of, int entries,
+                                  int experts, cudaStream_t stream) {
+  SPROUT_REQUIRE(ids && counts && offsets && sorted && place_of && entries > 0 && experts > 0 && experts <= 8192,
+                 "moe_arrange: bad arguments");
+  sprout_launch(moe_arrange_kernel, dim3(1), dim3(1024), (size_t)experts * sizeof(int), stream, ids, counts, offsets, sorted,
+                place_of, entries, experts);
+  return sprout_check_launch("moe_arrange");
+}
+
+SPROUT_API int sprout_moe_up_plain(const void* h, int h_stride, int dtype, const int* sorted, const int* offsets,
+                                   const void* w_gate_up, void* act, int max_rows, int experts, int top, int width, int ff,
+                                   float limit, float alpha, cudaStream_t stream) {
+  SPROUT_REQUIRE(h && sorted && offsets && w_gate_up && act && max_rows > 0 && experts > 0 && width > 0 && ff > 0,
+                 "moe_up: bad arguments");
+  SPROUT_REQUIRE(width <= 12000, "moe_up: width up to 12000");
+  dim3 grid(max_rows, ff >= 512 ? 4 : 1);
+  const size_t smem = (size_t)width * sizeof(float);
+  if (dtype == SPROUT_F32)
+    sprout_launch(moe_up_plain_kernel<float>, grid, dim3(256), smem, stream, (const float*)h, h_stride, sorted, offsets,
+                  (const float*)w_gate_up, (float*)act, experts, top, width, ff, limit, alpha);
+  else if (dtype == SPROUT_BF16)
+    sprout_launch(moe_up_plain_kernel<__nv_bfloat16>, grid, dim3(256), smem, stream, (const __nv_bfloat16*)h, h_stride, sorted,
+                  offsets, (const __nv_bfloat16*)w_gate_up, (__nv_bfloat16*)act, experts, top, width, ff, limit, alpha);
+  else
+    return sprout_fail("moe_up: unknown dtype %d", dtype);
+  return sprout_check_launch("moe_up_plain");
+}
+
+SPROUT_API int sprout_moe_down_plain(const void* act, int dtype, const int* offsets, const void* w_down, float* rows_out,
+                                     int max_rows, int experts, int width, int ff, cudaStream_t stream) {
+  SPROUT_REQUIRE(act && offsets && w_down && rows_out && max_rows > 0 && experts > 0 && width > 0 && ff > 0,
+                 "moe_down: bad arguments");
+  SPROUT_REQUIRE(ff <= 12000, "moe_down: expert size up to 12000");
+  dim3 grid(max_rows, width >= 512 ? 4 : 1);
+  const size_t smem = (size_t)ff * sizeof(float);
+  if (dtype == SPROUT_F32)
+    sprout_launch(moe_down_plain_kernel<float>, grid, dim3(256), smem, stream, (const float*)act, offsets,
+                  (const float*)w_down, rows_out, experts, width, ff);
+  else if (dtype == SPROUT_BF16)
+    sprout_launch(moe_down_plain_kernel<__nv_bfloat16>, grid, dim3(256), smem, stream, (const __nv_bfloat16*)act, offsets,
+                  (const __nv_bfloat16*)w_down, rows_out, experts, width, ff);
+  else
+    return sprout_fail("moe_down: unknown dtype %d", dtype);
+  return sprout_check_launch("moe_down_plain");
+}
+
+SPROUT_API int sprout_moe_combine(float* y, const void* h, int h_stride, int dtype, const int* ids, const float* weights,
+                                  const int* place_of, const float* rows, int tokens, int width, int top,
+                                  cudaStream_t stream) {
+  SPROUT_REQUIRE(y && h && ids && weights && place_of && tokens > 0 && width > 0 && top > 0, "moe_combine: bad arguments");
+  if (dtype == SPROUT_F32)
+    sprout_launch(moe_combine_kernel<float>, dim3(tokens), dim3(256), 0, stream, y, (const float*)h, h_stride, ids, weights,
+                  place_of, rows, width, top);
+  else if (dtype == SPROUT_BF16)
+    sprout_launch(moe_combine_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, stream, y, (const __nv_bfloat16*)h, h_stride,
+                  ids, weights, place_of, rows, width, top);
+  else
+    return sprout_fail("moe_combine: unknown dtype %d", dtype);
+  return sprout_check_launch("moe_combine");
+}

@@ -62,6 +62,19 @@ _SIGNATURES = {
     "sprout_latent_attention_mma_supported": [_I, _I],
     "sprout_depth_average": [_P, _P, _P, _I, _L, _P],
     "sprout_softcap": [_P, _F, _L, _P],
+    "sprout_layernorm": [_P, _P, _P, _I, _P, _I, _I, _F, _P],
+    "sprout_norm_add": [_P, _P, _P, _P, _P, _I, _I, _I, _F, _P],
+    "sprout_gated_rmsnorm": [_P, _P, _P, _I, _P, _I, _I, _I, _F, _P],
+    "sprout_relu2": [_P, _P, _I, _L, _P],
+    "sprout_glu_clamped": [_P, _P, _I, _I, _I, _F, _F, _P],
+    "sprout_rope_maps_append": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "sprout_multimap_attention_simple": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _P, _P],
+    "sprout_decay_scan": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+    "sprout_moe_route": [_P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
+    "sprout_moe_arrange": [_P, _P, _P, _P, _P, _I, _I, _P],
+    "sprout_moe_up_plain": [_P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _P],
+    "sprout_moe_down_plain": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
+    "sprout_moe_combine": [_P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _P],
 }
 
 _lock = threading.Lock()
@@ -1066,6 +1079,204 @@ def softcap(x, cap: float):
     if not x.is_contiguous():
         raise KernelError("softcap: x must be contiguous")
     _run("sprout_softcap", _ptr(x, "x", torch.float32), float(cap), x.numel(), _stream())
+
+
+# ---------------------------------------------------------------------------------- layers wrapped in two norms, activations
+
+def layernorm(x, gain, out, eps: float, rows=None):
+    """out[r] = (x[r] - mean) / sqrt(var + eps) * gain of row r (or of row rows[r]); x float32, out float32 or bfloat16."""
+    if x.dim() != 2 or out.dim() != 2 or not x.is_contiguous() or not out.is_contiguous():
+        raise KernelError("layernorm: x and out must be contiguous 2-D")
+    R, H = out.shape
+    if x.shape[1] != H or gain.numel() != H or (rows is None and x.shape[0] != R) or (rows is not None and rows.numel() != R):
+        raise KernelError("layernorm: shapes do not fit")
+    _run("sprout_layernorm", _ptr(x, "x", torch.float32), _ptr(gain, "gain", torch.float32), _ptr(out, "out"),
+         _dtype_code(out.dtype), _ptr(rows, "rows", torch.int32, allow_none=True), R, H, float(eps), _stream())
+
+
+def norm_add(y, gain, x, eps: float, next_gain=None, h=None):
+    """x += layernorm(y) * gain (float32, in place); with ``next_gain`` and ``h`` also h = layernorm(x) * next_gain of
+    the new x, in h's dtype: the norm after a sublayer, the residual sum and the norm before the next sublayer."""
+    if y.dim() != 2 or not y.is_contiguous() or not x.is_contiguous() or x.shape != y.shape or gain.numel() != y.shape[1]:
+        raise KernelError("norm_add: y and x must be contiguous [rows, width], gain [width]")
+    if (next_gain is None) != (h is None) or (h is not None and (h.shape != x.shape or not h.is_contiguous()
+                                                                   or next_gain.numel() != y.shape[1])):
+        raise KernelError("norm_add: the next norm's gain and its output go together and have x's width")
+    _run("sprout_norm_add", _ptr(y, "y", torch.float32), _ptr(gain, "gain", torch.float32), _ptr(x, "x", torch.float32),
+         _ptr(next_gain, "next_gain", torch.float32, True), _ptr(h, "h", allow_none=True),
+         _dtype_code(h.dtype) if h is not None else F32, y.shape[0], y.shape[1], float(eps), _stream())
+
+
+def gated_rmsnorm(o, gain, gate, out, eps: float):
+    """out = o / sqrt(mean(o^2) + eps) * gain * sigmoid(gate); o float32 [rows, width], gate a view [rows, width] with
+    unit inner stride of out's dtype."""
+    _rows_contiguous(gate, "gate")
+    if o.dim() != 2 or not o.is_contiguous() or not out.is_contiguous() or out.shape != o.shape or gate.shape != o.shape \
+            or gate.dtype != out.dtype or gain.numel() != o.shape[1]:
+        raise KernelError("gated_rmsnorm: shapes or dtypes do not fit")
+    _run("sprout_gated_rmsnorm", _ptr(o, "o", torch.float32), _ptr(gain, "gain", torch.float32), _ptr(gate, "gate"),
+         gate.stride(0), _ptr(out, "out"), _dtype_code(out.dtype), o.shape[0], o.shape[1], float(eps), _stream())
+
+
+def relu2(z, out):
+    """out = max(z, 0)^2 element by element."""
+    if not z.is_contiguous() or not out.is_contiguous() or z.shape != out.shape or z.dtype != out.dtype:
+        raise KernelError("relu2: z and out must be contiguous and alike")
+    _run("sprout_relu2", _ptr(z, "z"), _ptr(out, "out"), _dtype_code(z.dtype), z.numel(), _stream())
+
+
+def glu_clamped(gate_up, out, limit: float, alpha: float):
+    """out = g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit); rows of ``gate_up``
+    hold the gate values first and the up values after them."""
+    R, ff = out.shape
+    if not gate_up.is_contiguous() or not out.is_contiguous() or tuple(gate_up.shape) != (R, 2 * ff) or gate_up.dtype != out.dtype:
+        raise KernelError("glu_clamped: gate_up must be contiguous [rows, 2 ff] of out's dtype")
+    _run("sprout_glu_clamped", _ptr(gate_up, "gate_up"), _ptr(out, "out"), _dtype_code(out.dtype), R, ff, float(limit),
+         float(alpha), _stream())
+
+
+# ---------------------------------------------------------------------------------- attention with one or two maps per head
+
+def rope_maps_append(rows, positions, seq_of_token, block_table, cos_table, sin_table, k_cache, v_cache, q_vectors: int,
+                     kv_heads: int, maps: int, dim: int, vdim: int, page_tokens: int, write: bool, status):
+    """Rotate the first ``2 * cos_table.shape[1]`` elements of every query vector (in place) and key vector by the token's
+    position, half-split pairs; append keys ([pages, kv_heads, page_tokens, maps * dim]) and values
+    ([pages, kv_heads, page_tokens, vdim]) when ``write``.  A row holds q_vectors * dim query elements, then (when
+    ``write``) kv_heads * maps * dim key elements and kv_heads * vdim value elements."""
+    _rows_contiguous(rows, "rows")
+    _rows_contiguous(block_table, "block_table")
+    T = rows.shape[0]
+    cos_ptr, sin_ptr, max_positions, rot = _rotary(cos_table, sin_table, dim, "rope_maps_append")
+    if write:
+        if k_cache.dtype != rows.dtype or not k_cache.is_contiguous() or tuple(k_cache.shape[1:]) != (kv_heads, page_tokens, maps * dim):
+            raise KernelError("rope_maps_append: k_cache must be contiguous [pages, kv_heads, page_tokens, maps * dim]")
+        if v_cache.dtype != rows.dtype or not v_cache.is_contiguous() or tuple(v_cache.shape[1:]) != (kv_heads, page_tokens, vdim):
+            raise KernelError("rope_maps_append: v_cache must be contiguous [pages, kv_heads, page_tokens, vdim]")
+    _run("sprout_rope_maps_append", _ptr(rows, "rows"), rows.stride(0), _dtype_code(rows.dtype),
+         _ptr(positions, "positions", torch.int32), _ptr(seq_of_token, "seq_of_token", torch.int32),
+         _ptr(block_table, "block_table", torch.int32), block_table.stride(0), cos_ptr, sin_ptr, max_positions,
+         _ptr(k_cache, "k_cache", allow_none=not write), _ptr(v_cache, "v_cache", allow_none=not write), T, q_vectors,
+         kv_heads, maps, dim, rot, vdim, page_tokens, k_cache.shape[0] if write else 1, 1 if write else 0,
+         _ptr(status, "status", torch.int32), _stream())
+
+
+def multimap_attention_simple(q, cache, ctx, out, heads: int, kv_heads: int, maps: int, dim: int, vdim: int, scale: float,
+                              lam: float, norm_eps: float, out_scale: float, status):
+    """Causal attention with ``maps`` (1 or 2) softmax maps per head over shared values, float32 arithmetic:
+    out = (a_0 - lam a_1) [/ rms when norm_eps > 0] * out_scale per head.  q [tokens, heads * maps * dim] (a view with
+    unit inner stride), out [tokens, heads * vdim]."""
+    _rows_contiguous(q, "q")
+    _rows_contiguous(out, "out")
+    k_cache, v_cache = cache.k, cache.v
+    if k_cache.dtype != q.dtype or v_cache.dtype != q.dtype or out.dtype != q.dtype:
+        raise KernelError("multimap_attention: q, the cache and out must have one dtype")
+    if tuple(k_cache.shape[1:]) != (kv_heads, cache.page_tokens, maps * dim) or tuple(v_cache.shape[1:]) != (kv_heads, cache.page_tokens, vdim):
+        raise KernelError("multimap_attention: the cache's shape does not fit the heads")
+    if q.shape[1] != heads * maps * dim or out.shape[1] != heads * vdim or out.shape[0] != q.shape[0]:
+        raise KernelError("multimap_attention: q or out has the wrong width")
+    _run("sprout_multimap_attention_simple", _ptr(q, "q"), q.stride(0), _ptr(k_cache, "k_cache"), _ptr(v_cache, "v_cache"),
+         _ptr(cache.block_table, "block_table", torch.int32), cache.block_table.stride(0),
+         _ptr(ctx.seq_of_token, "seq_of_token", torch.int32), _ptr(ctx.positions, "positions", torch.int32), _ptr(out, "out"),
+         out.stride(0), _dtype_code(q.dtype), q.shape[0], heads, kv_heads, maps, dim, vdim, cache.page_tokens,
+         k_cache.shape[0], float(scale), float(lam), float(norm_eps), float(out_scale), _ptr(status, "status", torch.int32),
+         _stream())
+
+
+# ---------------------------------------------------------------------------------- linear attention with decay and state
+
+def decay_scan(rows, q_start, state_slots, state, decay, out, heads: int, dim: int, vdim: int, silu: bool, status):
+    """Per request and head, token by token: S = decay_h S + k v^T, o = S^T q, with q, k, v (after silu when ``silu``)
+    taken from ``rows`` [tokens, >= heads * (2 dim + vdim)] laid out [q | k | v]; ``state`` float32
+    [slots, heads, dim, vdim] is read and written at the requests' slots; out float32 [tokens, heads * vdim]."""
+    _rows_contiguous(rows, "rows")
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (heads, dim, vdim):
+        raise KernelError("decay_scan: state must be contiguous float32 [slots, heads, dim, vdim]")
+    if not out.is_contiguous() or tuple(out.shape) != (rows.shape[0], heads * vdim) or decay.numel() != heads:
+        raise KernelError("decay_scan: out must be contiguous float32 [tokens, heads * vdim], one decay per head")
+    _run("sprout_decay_scan", _ptr(rows, "rows"), rows.stride(0), _dtype_code(rows.dtype), _ptr(q_start, "q_start", torch.int32),
+         _ptr(state_slots, "state_slots", torch.int32), _ptr(state, "state", torch.float32), state.shape[0],
+         _ptr(decay, "decay", torch.float32), _ptr(out, "out", torch.float32), state_slots.numel(), heads, dim, vdim,
+         1 if silu else 0, _ptr(status, "status", torch.int32), _stream())
+
+
+# ---------------------------------------------------------------------------------- routed feed-forward
+
+def moe_route(h, router, correction, ids, weights, counts, experts: int, top: int, scale: float):
+    """Per token: softmax of the float32 router product, ``top`` largest of score + correction (lowest index first among
+    equals), weights = taken scores / (their sum + 1e-20) * scale.  ids int32 [tokens, top] (from ``experts`` on:
+    identity experts), weights float32 [tokens, top]; counts int32 [experts] += rows per real expert."""
+    _rows_contiguous(h, "h")
+    outputs, width = router.shape
+    T = h.shape[0]
+    if not router.is_contiguous() or h.shape[1] != width or correction.numel() != outputs or tuple(ids.shape) != (T, top) \
+            or tuple(weights.shape) != (T, top) or not ids.is_contiguous() or not weights.is_contiguous() or counts.numel() < max(experts, 1):
+        raise KernelError("moe_route: shapes do not fit")
+    _run("sprout_moe_route", _ptr(h, "h"), h.stride(0), _dtype_code(h.dtype), _ptr(router, "router", torch.float32),
+         _ptr(correction, "correction", torch.float32), _ptr(ids, "ids", torch.int32), _ptr(weights, "weights", torch.float32),
+         _ptr(counts, "counts", torch.int32), T, width, outputs, experts, top, float(scale), _stream())
+
+
+def moe_arrange(ids, counts, offsets, order, place_of, experts: int):
+    """counts -> offsets [experts + 1] (counts are zeroed again); every (token, place) of a real expert gets a row in its
+    expert's range: order[row] = token * top + place, place_of[token * top + place] = row (-1 for identity experts)."""
+    entries = ids.numel()
+    if offsets.numel() < experts + 1 or order.numel() < entries or place_of.numel() < entries:
+        raise KernelError("moe_arrange: buffers too small")
+    _run("sprout_moe_arrange", _ptr(ids, "ids", torch.int32), _ptr(counts, "counts", torch.int32),
+         _ptr(offsets, "offsets", torch.int32), _ptr(order, "order", torch.int32), _ptr(place_of, "place_of", torch.int32),
+         entries, experts, _stream())
+
+
+def moe_up_plain(h, order, offsets, w_gate_up, act, experts: int, top: int, limit: float, alpha: float):
+    """act[row] = glu_clamped(W_gate[e] a, W_up[e] a) for the arranged rows (a = h[order[row] // top], e the row's expert);
+    w_gate_up [experts, 2 ff, width] with gate rows first; CUDA cores, float32 sums in ascending k."""
+    _rows_contiguous(h, "h")
+    R, ff = act.shape
+    if not w_gate_up.is_contiguous() or tuple(w_gate_up.shape) != (experts, 2 * ff, h.shape[1]) or w_gate_up.dtype != h.dtype \
+            or act.dtype != h.dtype or not act.is_contiguous():
+        raise KernelError("moe_up: shapes or dtypes do not fit")
+    _run("sprout_moe_up_plain", _ptr(h, "h"), h.stride(0), _dtype_code(h.dtype), _ptr(order, "order", torch.int32),
+         _ptr(offsets, "offsets", torch.int32), _ptr(w_gate_up, "w_gate_up"), _ptr(act, "act"), R, experts, top, h.shape[1], ff,
+         float(limit), float(alpha), _stream())
+
+
+def moe_down_plain(act, offsets, w_down, rows_out, experts: int):
+    """rows_out[row] = W_down[e] act[row] (float32) for the arranged rows; w_down [experts, width, ff]."""
+    R, ff = act.shape
+    width = rows_out.shape[1]
+    if not w_down.is_contiguous() or tuple(w_down.shape) != (experts, width, ff) or w_down.dtype != act.dtype \
+            or rows_out.dtype != torch.float32 or not rows_out.is_contiguous() or rows_out.shape[0] != R or not act.is_contiguous():
+        raise KernelError("moe_down: shapes or dtypes do not fit")
+    _run("sprout_moe_down_plain", _ptr(act, "act"), _dtype_code(act.dtype), _ptr(offsets, "offsets", torch.int32),
+         _ptr(w_down, "w_down"), _ptr(rows_out, "rows_out", torch.float32), R, experts, width, ff, _stream())
+
+
+def moe_combine(y, h, ids, weights, place_of, rows, top: int):
+    """y[t] += sum over the token's places of weight * (h[t] for an identity expert, else rows[place_of])."""
+    _rows_contiguous(h, "h")
+    T, width = y.shape
+    if not y.is_contiguous() or y.dtype != torch.float32 or h.shape != y.shape or (rows is not None and rows.shape[1] != width):
+        raise KernelError("moe_combine: shapes do not fit")
+    _run("sprout_moe_combine", _ptr(y, "y", torch.float32), _ptr(h, "h"), h.stride(0), _dtype_code(h.dtype),
+         _ptr(ids, "ids", torch.int32), _ptr(weights, "weights", torch.float32), _ptr(place_of, "place_of", torch.int32),
+         _ptr(rows, "rows", torch.float32, True), T, width, top, _stream())
+
+
+def multimap_attention(q, cache, ctx, out, heads: int, kv_heads: int, maps: int, dim: int, vdim: int, scale: float, lam: float,
+                       norm_eps: float, out_scale: float, status):
+    """Attention with one or two maps per head: picks the kernel for the dtype and the sizes."""
+    multimap_attention_simple(q, cache, ctx, out, heads, kv_heads, maps, dim, vdim, scale, lam, norm_eps, out_scale, status)
+
+
+def decay_attention(rows, ctx, state, decay, out, heads: int, dim: int, vdim: int, silu: bool, status):
+    """Linear attention with decay over the step's tokens, from and into the requests' state slots."""
+    decay_scan(rows, ctx.q_start, state.slots, state.buffer, decay, out, heads, dim, vdim, silu, status)
+
+
+def moe_experts(h, order, offsets, w_gate_up, w_down, act, rows_out, experts: int, top: int, limit: float, alpha: float):
+    """The routed experts' two products over the arranged rows."""
+    moe_up_plain(h, order, offsets, w_gate_up, act, experts, top, limit, alpha)
+    moe_down_plain(act, offsets, w_down, rows_out, experts)
 
 
 def describe_status(word: int) -> str:

@@ -73,8 +73,8 @@ def registered_parts(category: str) -> tuple[str, ...]:
 @dataclass(frozen=True)
 class TensorDecl:
     """A checkpoint tensor that a part reads.  ``init`` tells the random-weights mode how to
-    fill it: ``matrix`` and ``bias`` are N(0, 0.02), ``gain`` is 1 + N(0, 0.02); ``pass_last`` and
-    ``polynomial`` are described in ``weights.random_init``."""
+    fill it: ``matrix`` and ``bias`` are N(0, 0.02), ``gain`` is 1 + N(0, 0.02); ``pass_last``,
+    ``polynomial`` and ``wide`` are described in ``weights.random_init``."""
     name: str
     shape: tuple[int, ...]
     init: str = "matrix"

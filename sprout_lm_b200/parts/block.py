@@ -107,3 +107,52 @@ class PostNormBlock(Part):
             finish(y, norm.gain, norm.eps)
         else:
             kernels.sum_norm(y, norm.gain, x, norm.eps)
+
+
+@register_part("block", "sandwich_norm")
+class SandwichNormBlock(Part):
+    """A norm before and after each sublayer: x += norm_1(mixer(norm_0(x))), then x += norm_3(ffn(norm_2(x))).
+    The stream and the sums are float32.  A layer without a feed-forward (``feed_forward.kind == "none"``) has the
+    first two norms only.  A sublayer adds its output into a zeroed float32 buffer; one kernel then norms that
+    buffer, adds it to the stream and, after the mixer, also makes what the feed-forward reads."""
+
+    def __init__(self, prefix: str, layer: LayerSpec):
+        self.has_ffn = layer.feed_forward.kind != "none"
+        if len(layer.norms) != (4 if self.has_ffn else 2):
+            raise ValueError("a sandwich_norm block has two norms per sublayer")
+        self.norms = [build_part("norm", spec, prefix) for spec in layer.norms]
+        for norm in self.norms:
+            if getattr(norm, "fused_kind", None) != "layernorm":
+                raise ValueError("a sandwich_norm block takes layer norms")
+        self.mixer = build_part("mixer", layer.mixer, prefix)
+        self.feed_forward = build_part("feed_forward", layer.feed_forward, prefix) if self.has_ffn else None
+
+    def parts(self):
+        return [*self.norms, self.mixer, *([self.feed_forward] if self.has_ffn else [])]
+
+    def tensor_decls(self):
+        return [decl for part in self.parts() for decl in part.tensor_decls()]
+
+    def load(self, source):
+        for part in self.parts():
+            part.load(source)
+        self.dtype = source.runtime.dtype
+
+    def forward(self, x, ctx, cache, state):
+        import torch
+        from .. import kernels
+        before, after = self.norms[0], self.norms[1]
+        y = torch.zeros_like(x)
+        self.mixer.forward(before.forward(x), y, ctx, cache, state)
+        if not self.has_ffn:
+            kernels.norm_add(y, after.gain, x, after.eps)
+            return
+        if self.norms[2].eps == after.eps:
+            h = torch.empty(x.shape, dtype=self.dtype, device=x.device)
+            kernels.norm_add(y, after.gain, x, after.eps, next_gain=self.norms[2].gain, h=h)
+        else:
+            kernels.norm_add(y, after.gain, x, after.eps)
+            h = self.norms[2].forward(x)
+        y.zero_()
+        self.feed_forward.forward(h, y, ctx)
+        kernels.norm_add(y, self.norms[3].gain, x, self.norms[3].eps)

@@ -1,0 +1,96 @@
+"""Grouped-query attention whose heads hold one or two softmax maps over shared values (two: differential
+attention), on the paged cache.
+
+With ``maps`` = 2 a query head has two query vectors and a key/value head two key vectors of ``dim`` elements, laid
+out head by head as [map 0, map 1], and one value vector of ``value_dim`` elements.  Each map is a causal softmax
+attention of its own (score = scale * q . k) over the head's values; the head's output is
+a_0 - lambda * a_1 with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff (one number per layer, learned vectors of
+``dim`` elements), divided by its root mean square over the head's values (``norm_eps``; no weight) and multiplied by
+``out_scale``.  The first ``2 * table width`` elements of every query and key vector are rotated by the position.
+The cache keeps a key/value head's maps side by side in one key row (rotated) and its value row.
+
+A layer may read the keys and values another layer cached (its run-order entry has ``writes_cache=False``): it then
+has no key and value projections, only queries, lambda vectors and the output projection of its own.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import kernels
+from ..config.specs import PartSpec
+from .base import CacheSpec, CacheView, Part, TensorDecl, WeightSource, build_part, register_part
+from .linear import Linear
+
+DEFAULT_NAMES = {"q": "q", "k": "k", "v": "v", "o": "o", "lq1": "lq1", "lk1": "lk1", "lq2": "lq2", "lk2": "lk2"}
+
+
+@register_part("mixer", "multimap_attention")
+class MultiMapAttention(Part):
+    def __init__(self, prefix: str, hidden_size: int, heads: int, kv_heads: int, dim: int, value_dim: int, scale: float,
+                 position: PartSpec, maps: int = 2, diff: float = 0.0, norm_eps: float = 0.0, out_scale: float = 1.0,
+                 own_kv: bool = True, names: dict | None = None):
+        if heads <= 0 or kv_heads <= 0 or heads % kv_heads:
+            raise ValueError(f"multimap_attention: heads ({heads}) must be a positive multiple of kv_heads ({kv_heads})")
+        if maps not in (1, 2):
+            raise ValueError("multimap_attention: one or two maps per head")
+        if dim <= 0 or value_dim <= 0 or value_dim > 256:
+            raise ValueError("multimap_attention: dim must be positive and value_dim at most 256")
+        self.hidden_size, self.heads, self.kv_heads, self.dim, self.value_dim = hidden_size, heads, kv_heads, dim, value_dim
+        self.maps, self.scale, self.diff = maps, float(scale), float(diff)
+        self.norm_eps, self.out_scale, self.own_kv = float(norm_eps), float(out_scale), bool(own_kv)
+        self.names = {key: prefix + value for key, value in {**DEFAULT_NAMES, **(names or {})}.items()}
+        self.position = build_part("position", position)
+        self.q_width = heads * maps * dim
+        self.k_width = kv_heads * maps * dim
+        self.v_width = kv_heads * value_dim
+        self.lam = 0.0
+        self.runtime = None
+
+    def cache_spec(self):
+        return CacheSpec(kv_heads=self.kv_heads, head_dim=self.maps * self.dim, kind="full", value_dim=self.value_dim)
+
+    def state_spec(self):
+        return None
+
+    def tensor_decls(self):
+        n = self.names
+        decls = [TensorDecl(n["q"], (self.q_width, self.hidden_size))]
+        if self.own_kv:
+            decls += [TensorDecl(n["k"], (self.k_width, self.hidden_size)), TensorDecl(n["v"], (self.v_width, self.hidden_size))]
+        if self.maps == 2:
+            decls += [TensorDecl(n[key], (self.dim,), "wide") for key in ("lq1", "lk1", "lq2", "lk2")]
+        decls.append(TensorDecl(n["o"], (self.hidden_size, self.heads * self.value_dim)))
+        return decls
+
+    def load(self, source: WeightSource):
+        n, status = self.names, source.runtime.status
+        self.runtime = source.runtime
+        keys = ("q", "k", "v") if self.own_kv else ("q",)
+        fused = torch.cat([source.raw(n[key]) for key in keys], dim=0)
+        self.qkv = Linear(source.to_device_matrix(fused), None, status, any_inner_size=True)
+        self.out = Linear(source.matrix(n["o"]), None, status, any_inner_size=True)
+        if self.maps == 2:
+            lq1, lk1, lq2, lk2 = (source.raw(n[key]).to(torch.float32) for key in ("lq1", "lk1", "lq2", "lk2"))
+            # one number per layer, in float32 as the other 32-bit quantities
+            self.lam = float(torch.exp(torch.sum(lq1 * lk1)) - torch.exp(torch.sum(lq2 * lk2)) + torch.tensor(self.diff, dtype=torch.float32))
+        self.tables = self.position.rotary_tables(source.runtime)
+        if self.tables is not None and 2 * self.tables[0].shape[1] > self.dim:
+            raise ValueError("multimap_attention: the rotation is wider than a query vector")
+
+    def forward(self, h, x, ctx, cache: CacheView, state=None):
+        """x (float32) += W_o attention(h); appends this step's keys and values when the cache slot is this layer's."""
+        if cache.write != self.own_kv:
+            raise RuntimeError("multimap_attention: a layer with key and value projections of its own writes its cache slot, "
+                               "a layer without them reads another layer's")
+        status = self.runtime.status
+        cos, sin = self.tables if self.tables is not None else (None, None)
+        rows = self.qkv.forward(h)
+        kernels.rope_maps_append(rows, ctx.positions, ctx.seq_of_token, cache.block_table, cos, sin, cache.k, cache.v,
+                                 self.heads * self.maps, self.kv_heads, self.maps, self.dim, self.value_dim, cache.page_tokens,
+                                 cache.write, status)
+        attended = torch.empty((rows.shape[0], self.heads * self.value_dim), dtype=rows.dtype, device=rows.device)
+        kernels.multimap_attention(rows[:, :self.q_width], cache, ctx, attended, self.heads, self.kv_heads, self.maps, self.dim,
+                                   self.value_dim, self.scale, self.lam, self.norm_eps, self.out_scale, status)
+        self.out.forward(attended, residual=x)

@@ -37,3 +37,31 @@ class RMSNorm(Part):
         out = torch.empty((count, self.size), dtype=self.out_dtype, device=x.device)
         kernels.rmsnorm(x, self.gain, out, self.eps, rows)
         return out
+
+
+@register_part("norm", "layernorm")
+class LayerNorm(Part):
+    """out = (x - mean) / sqrt(var + eps) * w, var the mean of the squared deviations; a weight and no bias.
+    float32 arithmetic; the output has the compute dtype."""
+    fused_kind = "layernorm"     # a block that sums and norms in one kernel may take gain and eps
+
+    def __init__(self, prefix: str, size: int, eps: float, name: str = "norm", suffix: str = ""):
+        if eps <= 0:
+            raise ValueError("layernorm: eps must be positive")
+        self.size, self.eps = int(size), float(eps)
+        self.tensor_name = f"{prefix}{name}{suffix}"
+        self.gain = None
+        self.out_dtype = None
+
+    def tensor_decls(self):
+        return [TensorDecl(self.tensor_name, (self.size,), "gain")]
+
+    def load(self, source: WeightSource):
+        self.gain = source.vector(self.tensor_name)
+        self.out_dtype = source.runtime.dtype
+
+    def forward(self, x: torch.Tensor, rows: torch.Tensor | None = None) -> torch.Tensor:
+        count = x.shape[0] if rows is None else rows.numel()
+        out = torch.empty((count, self.size), dtype=self.out_dtype, device=x.device)
+        kernels.layernorm(x, self.gain, out, self.eps, rows)
+        return out

@@ -116,3 +116,31 @@ class ScaledHalfSplitRotary(_Rotary):
     """Pairs (i, i + dims / 2); with ``scaling`` (factor, original, fast, slow) the frequencies are those of
     ``yarn_frequencies`` and cos and sin are multiplied by 0.1 ln(factor) + 1."""
     interleaved = False
+
+
+@register_part("position", "rope_linear")
+class LinearScaledRotary(Part):
+    """Pairs (i, i + dims / 2) over the first ``dims`` elements, angle = position * theta**(-2i / dims) / factor
+    (``factor`` 1: no scaling).  Tables as the other rotations keep them: float64 on the host, float32 on the device,
+    one copy per set of constants."""
+    interleaved = False
+
+    def __init__(self, prefix: str, dims: int, theta: float, max_positions: int, factor: float = 1.0):
+        if dims <= 0 or dims % 2:
+            raise ValueError("rotary position encoding needs an even, positive number of elements")
+        if theta <= 0 or max_positions <= 0 or factor <= 0:
+            raise ValueError("rotary position encoding needs positive theta, max_positions and factor")
+        self.dims, self.theta, self.max_positions, self.factor = int(dims), float(theta), int(max_positions), float(factor)
+
+    def frequencies(self) -> np.ndarray:
+        return self.theta ** (-2.0 * np.arange(self.dims // 2, dtype=np.float64) / self.dims) / self.factor
+
+    def rotary_tables(self, runtime):
+        def build():
+            angle = np.arange(self.max_positions, dtype=np.float64)[:, None] * self.frequencies()[None, :]
+            cos = torch.from_numpy(np.cos(angle).astype(np.float32)).to(runtime.device)
+            sin = torch.from_numpy(np.sin(angle).astype(np.float32)).to(runtime.device)
+            return cos.contiguous(), sin.contiguous()
+        key = ("rope_linear", self.dims, self.theta, self.max_positions, self.factor)
+        shared = getattr(runtime, "shared", None)
+        return shared(key, build) if shared else build()
