@@ -64,29 +64,54 @@ def attention_keys_values(h, weights, prefix, m, positions):
     return k, v
 
 
+def differential_heads(q, k, v, positions, scale, lam, eps, out_scale):
+    """q [T, H, 2, dim] (rotated), k [S, G, 2, dim] (rotated; key j sits at position j), v [S, G, vdim]:
+    per head a_0 - lam a_1 over the keys j <= position, divided by its root mean square, times out_scale.
+    Returns [T, H, vdim]."""
+    T, H = q.shape[:2]
+    G = k.shape[1]
+    visible = np.asarray(positions)[:, None] >= np.arange(k.shape[0])[None, :]
+    out = np.zeros((T, H, v.shape[-1]))
+    for head in range(H):
+        g = head // (H // G)
+        maps = []
+        for which in range(2):
+            score = (q[:, head, which, :] @ k[:, g, which, :].T) * scale
+            score = np.where(visible, score, -np.inf)
+            maps.append(softmax(score) @ v[:, g, :])
+        out[:, head] = rms(maps[0] - lam * maps[1], eps) * out_scale
+    return out
+
+
+def differential_lambda(weights, prefix, diff):
+    return np.exp(np.sum(weights[prefix + "lq1"] * weights[prefix + "lk1"])) \
+        - np.exp(np.sum(weights[prefix + "lq2"] * weights[prefix + "lk2"])) + diff
+
+
 def differential_attention(h, weights, prefix, m, eps, k, v, positions=None):
     """Two softmax maps per head over the same values; o = a1 - lambda a2, divided by its root mean
     square over the head, times (1 - diff); then the output projection.  ``k``/``v``: all keys and
     values of the sequence (own or another layer's)."""
     T = h.shape[0]
-    H, G, dim, vdim = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, dim = m["heads"], m["dim"]
     positions = np.arange(T) if positions is None else positions
     q = (h @ weights[prefix + "q"].T).reshape(T, H * 2, dim)
     q = rotate(q, positions, m["rot"]).reshape(T, H, 2, dim)
-    lam = np.exp(np.sum(weights[prefix + "lq1"] * weights[prefix + "lk1"])) \
-        - np.exp(np.sum(weights[prefix + "lq2"] * weights[prefix + "lk2"])) + m["diff"]
-    visible = np.asarray(positions)[:, None] >= np.arange(k.shape[0])[None, :]
-    heads = []
-    for head in range(H):
-        g = head // (H // G)
-        maps = []
-        for which in range(2):
-            score = (q[:, head, which, :] @ k[:, g, which, :].T) * m["scale"]
-            score = np.where(visible, score, -np.inf)
-            maps.append(softmax(score) @ v[:, g, :])
-        o = maps[0] - lam * maps[1]
-        heads.append(rms(o, eps) * (1.0 - m["diff"]))
-    return np.concatenate(heads, axis=-1) @ weights[prefix + "o"].T
+    lam = differential_lambda(weights, prefix, m["diff"])
+    o = differential_heads(q, k, v, positions, m["scale"], lam, eps, 1.0 - m["diff"])
+    return o.reshape(T, -1) @ weights[prefix + "o"].T
+
+
+def decay_recurrence(q, k, v, decay, state=None):
+    """q, k [T, H, dim], v [T, H, vdim]: S = decay_h S + k v^T, o = S^T q token by token.  (o [T, H, vdim], S)."""
+    T, H, dim = q.shape
+    S = np.zeros((H, dim, v.shape[-1])) if state is None else state.copy()
+    out = np.zeros((T, H, v.shape[-1]))
+    decay = np.asarray(decay, dtype=np.float64)
+    for t in range(T):
+        S = decay[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
+        out[t] = np.einsum("hdv,hd->hv", S, q[t])
+    return out, S
 
 
 def lightning(h, weights, prefix, m, eps, state=None):
@@ -98,12 +123,7 @@ def lightning(h, weights, prefix, m, eps, state=None):
     q = silu(h @ weights[prefix + "q"].T).reshape(T, H, dim)
     k = silu(h @ weights[prefix + "k"].T).reshape(T, H, dim)
     v = silu(h @ weights[prefix + "v"].T).reshape(T, H, vdim)
-    S = np.zeros((H, dim, vdim)) if state is None else state.copy()
-    out = np.zeros((T, H, vdim))
-    decay = np.asarray(m["decay"], dtype=np.float64)
-    for t in range(T):
-        S = decay[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
-        out[t] = np.einsum("hdv,hd->hv", S, q[t])
+    out, S = decay_recurrence(q, k, v, m["decay"], state)
     o = rms(out.reshape(T, H * vdim), eps) * weights[prefix + "norm"]
     o = o * sigmoid(h @ weights[prefix + "g"].T)
     return o @ weights[prefix + "o"].T, S
@@ -182,3 +202,43 @@ def forward(config, weights, tokens, return_layers=False):
         after.append(x)
     logits = layer_norm(x, weights["final.norm"], eps) @ weights["head"].T
     return (logits, np.stack(after)) if return_layers else logits
+
+
+# ------------------------------------------------------------------------------ model folders
+def read_model_folder(directory):
+    """(config, weights as float64) of a folder with config.json and model.safetensors (its own little reader: an
+    8-byte length, a JSON header, the data)."""
+    import json
+    import struct
+    from pathlib import Path
+    directory = Path(directory)
+    config = json.loads((directory / "config.json").read_text())
+    raw = (directory / "model.safetensors").read_bytes()
+    size = struct.unpack("<Q", raw[:8])[0]
+    header = json.loads(raw[8:8 + size])
+    data = raw[8 + size:]
+    weights = {}
+    for name, info in header.items():
+        if name == "__metadata__":
+            continue
+        begin, end = info["data_offsets"]
+        chunk = data[begin:end]
+        if info["dtype"] == "BF16":
+            values = (np.frombuffer(chunk, dtype="<u2").astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+        elif info["dtype"] == "F32":
+            values = np.frombuffer(chunk, dtype="<f4").astype(np.float64)
+        else:
+            raise ValueError(f"{name}: dtype {info['dtype']}")
+        weights[name] = values.reshape(info["shape"])
+    return config, weights
+
+
+def logits(config, weights, tokens):
+    return forward(config, weights, tokens)
+
+
+def greedy(config, weights, prompt, count):
+    tokens = list(prompt)
+    for _ in range(count):
+        tokens.append(int(np.argmax(forward(config, weights, tokens)[-1])))
+    return tokens[len(prompt):]
