@@ -13,7 +13,16 @@
 //  * multimap_attention_simple: one block per (token, query head); keys in chunks of 128 aligned to
 //                               absolute position with running maxima and sums: what is done for a query
 //                               does not depend on how the tokens were cut into steps.
-#include "common.cuh"
+//  * multimap_attention_mma:    bfloat16 on tensor cores (`mma.sync.m16n8k16`): a CTA of 4 warps owns 64
+//                               (token, head of one key/value group) rows of a request and walks the keys in
+//                               tiles of 64 through a double-buffered cp.async ring; a warp holds both maps of
+//                               its 16 rows (scores, running maxima and sums, output accumulators per map; the
+//                               value tile is read once from memory for both), so the difference, the norm over
+//                               the head and the scale happen on the accumulators.  Prompt portions and single
+//                               tokens of a mixed batch in one launch.
+#include "attention_bf16.cuh"
+
+using namespace sprout_attn;
 
 namespace {
 
@@ -175,7 +184,292 @@ multimap_attention_simple_kernel(const T* __restrict__ q, int q_stride, const T*
     if (tid + part * CHUNK < vdim) dst[tid + part * CHUNK] = from_float<T>(o[part] * factor);
 }
 
+
+// ------------------------------------------------------------------------------------------ tensor cores
+constexpr int MM_ROWS = 64, MM_KEYS = 64, MM_THREADS = 128;
+
+struct MultiMapParams {
+  const __nv_bfloat16* q; int q_stride;
+  const __nv_bfloat16* k_cache; const __nv_bfloat16* v_cache;
+  const int* block_table; int table_stride;
+  const int* q_start; const int* positions;
+  __nv_bfloat16* out; int out_stride;
+  int requests, heads, kv_heads, page_tokens, num_pages;
+  float scale, lambda, norm_eps, out_scale;
+  int* status;
+};
+
+template <int DIM, int VDIM, int MAPS>
+__global__ void __launch_bounds__(MM_THREADS)
+multimap_attention_mma_kernel(const MultiMapParams p) {
+  constexpr int KW = MAPS * DIM, KSTRIDE = KW + 8, VSTRIDE = VDIM + 8, KCHUNKS = KW / 8, VCHUNKS = VDIM / 8;
+  extern __shared__ __align__(16) unsigned char mm_smem[];
+  __nv_bfloat16* sQ = (__nv_bfloat16*)mm_smem;                   // MM_ROWS x KSTRIDE
+  __nv_bfloat16* sK = sQ + MM_ROWS * KSTRIDE;                    // 2 x MM_KEYS x KSTRIDE
+  __nv_bfloat16* sV = sK + 2 * MM_KEYS * KSTRIDE;                // 2 x MM_KEYS x VSTRIDE
+  __shared__ int s_token[MM_ROWS], s_head[MM_ROWS], s_limit[MM_ROWS];
+  __shared__ long long s_row[2][MM_KEYS];
+
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = blockIdx.y, group = p.heads / p.kv_heads;
+  int tile = blockIdx.x, r = 0;
+  for (; r < p.requests; r++) {
+    const int tiles = ((p.q_start[r + 1] - p.q_start[r]) * group + MM_ROWS - 1) / MM_ROWS;
+    if (tile < tiles) {
+      tile = (tile & 1) ? tiles - 1 - (tile >> 1) : (tile >> 1);     // long and short causal tiles in turn
+      break;
+    }
+    tile -= tiles;
+  }
+  if (r >= p.requests) return;
+  const int q0 = p.q_start[r], rows_total = (p.q_start[r + 1] - q0) * group, row_base = tile * MM_ROWS;
+  const int* table = p.block_table + (size_t)r * p.table_stride;
+  if (tid < MM_ROWS) {
+    const int gi = row_base + tid;
+    if (gi < rows_total) {
+      const int tok = q0 + gi / group;
+      s_token[tid] = tok;
+      s_head[tid] = g * group + gi % group;
+      s_limit[tid] = p.positions[tok];
+    } else {
+      s_token[tid] = -1; s_head[tid] = 0; s_limit[tid] = -1;
+    }
+  }
+  __syncthreads();
+  const int last_row = min(rows_total, row_base + MM_ROWS) - 1 - row_base;
+  const int max_limit = s_limit[last_row];                          // positions grow with the row index
+  const int kv_tiles = max_limit / MM_KEYS + 1;
+
+  for (int idx = tid; idx < MM_ROWS * KCHUNKS; idx += MM_THREADS) {
+    const int row = idx / KCHUNKS, c = idx % KCHUNKS;
+    __nv_bfloat16* dst = sQ + row * KSTRIDE + c * 8;
+    if (s_token[row] >= 0) cp_async16(dst, p.q + (size_t)s_token[row] * p.q_stride + (size_t)s_head[row] * KW + c * 8);
+    else *(uint4*)dst = make_uint4(0, 0, 0, 0);
+  }
+  auto find_rows = [&](int t, int buf) {
+    if (tid < MM_KEYS) {
+      const int key = t * MM_KEYS + tid;
+      long long row = -1;
+      if (key <= max_limit) {
+        const int page = table[key / p.page_tokens];
+        if (page < 0 || page >= p.num_pages) atomicOr(p.status, SPROUT_STATUS_BAD_PAGE);
+        else row = ((long long)page * p.kv_heads + g) * p.page_tokens + key % p.page_tokens;
+      }
+      s_row[buf][tid] = row;
+    }
+  };
+  auto load_tile = [&](int buf) {
+    for (int idx = tid; idx < MM_KEYS * KCHUNKS; idx += MM_THREADS) {
+      const int row = idx / KCHUNKS, c = idx % KCHUNKS;
+      const long long at = s_row[buf][row];
+      __nv_bfloat16* dst = sK + (buf * MM_KEYS + row) * KSTRIDE + c * 8;
+      if (at >= 0) cp_async16(dst, p.k_cache + at * KW + c * 8);
+      else *(uint4*)dst = make_uint4(0, 0, 0, 0);
+    }
+    for (int idx = tid; idx < MM_KEYS * VCHUNKS; idx += MM_THREADS) {
+      const int row = idx / VCHUNKS, c = idx % VCHUNKS;
+      const long long at = s_row[buf][row];
+      __nv_bfloat16* dst = sV + (buf * MM_KEYS + row) * VSTRIDE + c * 8;
+      if (at >= 0) cp_async16(dst, p.v_cache + at * VDIM + c * 8);
+      else *(uint4*)dst = make_uint4(0, 0, 0, 0);
+    }
+  };
+  find_rows(0, 0);
+  __syncthreads();
+  load_tile(0);
+  cp_async_commit();
+
+  const int gr = lane >> 2, qc = lane & 3;
+  const int my_row0 = warp * 16 + gr, my_row1 = my_row0 + 8;
+  const int limit0 = s_limit[my_row0], limit1 = s_limit[my_row1];
+  float m0[MAPS], m1[MAPS], l0[MAPS], l1[MAPS];
+  float o[MAPS][VDIM / 8][4];
+#pragma unroll
+  for (int m = 0; m < MAPS; m++) {
+    m0[m] = m1[m] = -INFINITY;
+    l0[m] = l1[m] = 0.f;
+#pragma unroll
+    for (int i = 0; i < VDIM / 8; i++) o[m][i][0] = o[m][i][1] = o[m][i][2] = o[m][i][3] = 0.f;
+  }
+  const float scale_log2 = p.scale * 1.4426950408889634f;
+  const int warp_min_limit = s_limit[min(warp * 16, last_row)];
+
+  for (int t = 0; t < kv_tiles; t++) {
+    const int buf = t & 1;
+    if (t + 1 < kv_tiles) find_rows(t + 1, buf ^ 1);
+    __syncthreads();                                   // rows visible; everyone is done with buffer buf ^ 1
+    if (t + 1 < kv_tiles) load_tile(buf ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();                                // tile t (and Q) have landed
+    __syncthreads();
+    const __nv_bfloat16* tK = sK + buf * MM_KEYS * KSTRIDE;
+    const __nv_bfloat16* tV = sV + buf * MM_KEYS * VSTRIDE;
+    const int kv0 = t * MM_KEYS;
+    if (kv0 > s_limit[min(warp * 16 + 15, last_row)]) continue;       // no row of this warp sees the tile
+#pragma unroll
+    for (int m = 0; m < MAPS; m++) {
+      float s[MM_KEYS / 8][4];
+#pragma unroll
+      for (int i = 0; i < MM_KEYS / 8; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < DIM / 16; kk++) {
+        uint32_t a[4];
+        ldmatrix_x4(a, sQ + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KSTRIDE + m * DIM + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+        for (int n2 = 0; n2 < MM_KEYS / 16; n2++) {
+          uint32_t b[4];
+          ldmatrix_x4(b, tK + (n2 * 16 + (lane & 7) + (lane >> 4) * 8) * KSTRIDE + m * DIM + kk * 16 + ((lane >> 3) & 1) * 8);
+          mma_bf16(s[2 * n2], a, b[0], b[1]);
+          mma_bf16(s[2 * n2 + 1], a, b[2], b[3]);
+        }
+      }
+      float t_max0 = -INFINITY, t_max1 = -INFINITY;
+      if (kv0 + MM_KEYS - 1 > warp_min_limit) {
+#pragma unroll
+        for (int i = 0; i < MM_KEYS / 8; i++) {
+          const int key = kv0 + i * 8 + qc * 2;
+          if (key > limit0) s[i][0] = -INFINITY;
+          if (key + 1 > limit0) s[i][1] = -INFINITY;
+          if (key > limit1) s[i][2] = -INFINITY;
+          if (key + 1 > limit1) s[i][3] = -INFINITY;
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < MM_KEYS / 8; i++) {
+        t_max0 = fmaxf(t_max0, fmaxf(s[i][0], s[i][1]));
+        t_max1 = fmaxf(t_max1, fmaxf(s[i][2], s[i][3]));
+      }
+      t_max0 = fmaxf(t_max0, __shfl_xor_sync(0xffffffffu, t_max0, 1));
+      t_max0 = fmaxf(t_max0, __shfl_xor_sync(0xffffffffu, t_max0, 2));
+      t_max1 = fmaxf(t_max1, __shfl_xor_sync(0xffffffffu, t_max1, 1));
+      t_max1 = fmaxf(t_max1, __shfl_xor_sync(0xffffffffu, t_max1, 2));
+      const float n0 = fmaxf(m0[m], t_max0), n1 = fmaxf(m1[m], t_max1);     // running maxima of the unscaled scores
+      const float base0 = n0 == -INFINITY ? 0.f : n0 * scale_log2, base1 = n1 == -INFINITY ? 0.f : n1 * scale_log2;
+      const float alpha0 = m0[m] == -INFINITY ? 0.f : exp2f(m0[m] * scale_log2 - base0);
+      const float alpha1 = m1[m] == -INFINITY ? 0.f : exp2f(m1[m] * scale_log2 - base1);
+      m0[m] = n0; m1[m] = n1;
+      l0[m] *= alpha0; l1[m] *= alpha1;
+#pragma unroll
+      for (int i = 0; i < VDIM / 8; i++) { o[m][i][0] *= alpha0; o[m][i][1] *= alpha0; o[m][i][2] *= alpha1; o[m][i][3] *= alpha1; }
+#pragma unroll
+      for (int i = 0; i < MM_KEYS / 8; i++) {
+        s[i][0] = exp2f(fmaf(s[i][0], scale_log2, -base0)); s[i][1] = exp2f(fmaf(s[i][1], scale_log2, -base0));
+        s[i][2] = exp2f(fmaf(s[i][2], scale_log2, -base1)); s[i][3] = exp2f(fmaf(s[i][3], scale_log2, -base1));
+        l0[m] += s[i][0] + s[i][1];
+        l1[m] += s[i][2] + s[i][3];
+      }
+#pragma unroll
+      for (int kk = 0; kk < MM_KEYS / 16; kk++) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int d2 = 0; d2 < VDIM / 16; d2++) {
+          uint32_t b[4];
+          ldmatrix_x4_trans(b, tV + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VSTRIDE + d2 * 16 + (lane >> 4) * 8);
+          mma_bf16(o[m][2 * d2], a, b[0], b[1]);
+          mma_bf16(o[m][2 * d2 + 1], a, b[2], b[3]);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+
+  // per row: a_0 - lambda a_1, the norm over the head's values (the quad holds a row), the scale
+  float inv0[MAPS], inv1[MAPS];
+#pragma unroll
+  for (int m = 0; m < MAPS; m++) {
+    l0[m] += __shfl_xor_sync(0xffffffffu, l0[m], 1); l0[m] += __shfl_xor_sync(0xffffffffu, l0[m], 2);
+    l1[m] += __shfl_xor_sync(0xffffffffu, l1[m], 1); l1[m] += __shfl_xor_sync(0xffffffffu, l1[m], 2);
+    inv0[m] = 1.0f / l0[m];
+    inv1[m] = 1.0f / l1[m];
+  }
+  float sq0 = 0.f, sq1 = 0.f;
+#pragma unroll
+  for (int i = 0; i < VDIM / 8; i++) {
+#pragma unroll
+    for (int c = 0; c < 2; c++) {
+      float v0 = o[0][i][c] * inv0[0], v1 = o[0][i][2 + c] * inv1[0];
+      if (MAPS == 2) {
+        v0 -= p.lambda * (o[MAPS - 1][i][c] * inv0[MAPS - 1]);
+        v1 -= p.lambda * (o[MAPS - 1][i][2 + c] * inv1[MAPS - 1]);
+      }
+      o[0][i][c] = v0;
+      o[0][i][2 + c] = v1;
+      sq0 = fmaf(v0, v0, sq0);
+      sq1 = fmaf(v1, v1, sq1);
+    }
+  }
+  float f0 = p.out_scale, f1 = p.out_scale;
+  if (p.norm_eps > 0.f) {
+    sq0 += __shfl_xor_sync(0xffffffffu, sq0, 1); sq0 += __shfl_xor_sync(0xffffffffu, sq0, 2);
+    sq1 += __shfl_xor_sync(0xffffffffu, sq1, 1); sq1 += __shfl_xor_sync(0xffffffffu, sq1, 2);
+    f0 *= 1.0f / sqrtf(sq0 / (float)VDIM + p.norm_eps);
+    f1 *= 1.0f / sqrtf(sq1 / (float)VDIM + p.norm_eps);
+  }
+  if (s_token[my_row0] >= 0) {
+    __nv_bfloat16* dst = p.out + (size_t)s_token[my_row0] * p.out_stride + (size_t)s_head[my_row0] * VDIM + qc * 2;
+#pragma unroll
+    for (int i = 0; i < VDIM / 8; i++) *(__nv_bfloat162*)(dst + i * 8) = __floats2bfloat162_rn(o[0][i][0] * f0, o[0][i][1] * f0);
+  }
+  if (s_token[my_row1] >= 0) {
+    __nv_bfloat16* dst = p.out + (size_t)s_token[my_row1] * p.out_stride + (size_t)s_head[my_row1] * VDIM + qc * 2;
+#pragma unroll
+    for (int i = 0; i < VDIM / 8; i++) *(__nv_bfloat162*)(dst + i * 8) = __floats2bfloat162_rn(o[0][i][2] * f1, o[0][i][3] * f1);
+  }
+}
+
+template <int DIM, int VDIM, int MAPS>
+int launch_multimap(const MultiMapParams& p, int grid_x, cudaStream_t stream) {
+  const int smem = (3 * MM_ROWS * (MAPS * DIM + 8) + 2 * MM_KEYS * (VDIM + 8)) * 2;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(multimap_attention_mma_kernel<DIM, VDIM, MAPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (err != cudaSuccess) return sprout_fail("multimap_attention_mma: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(err));
+    configured = true;
+  }
+  sprout_launch(multimap_attention_mma_kernel<DIM, VDIM, MAPS>, dim3(grid_x, p.kv_heads), dim3(MM_THREADS), smem, stream, p);
+  return sprout_check_launch("multimap_attention_mma");
+}
+
+bool mma_sizes(int maps, int dim, int vdim) {
+  return (maps == 1 || maps == 2) && ((dim == 32 && vdim == 64) || (dim == 64 && vdim == 64) || (dim == 64 && vdim == 128) ||
+                                      (dim == 128 && vdim == 128) || (dim == 16 && vdim == 32) || (dim == 32 && vdim == 32));
+}
+
 }  // namespace
+
+SPROUT_API int sprout_multimap_attention_mma_supported(int maps, int dim, int vdim) { return mma_sizes(maps, dim, vdim) ? 1 : 0; }
+
+// bfloat16 only.  `tiles` bounds the (request, 64 rows) tiles of the batch: sum over requests of
+// ceil(tokens * heads / kv_heads / 64), or any larger number.
+SPROUT_API int sprout_multimap_attention_mma(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                                             const int* block_table, int table_stride, const int* q_start,
+                                             const int* positions, void* out, int out_stride, int requests, int tiles,
+                                             int heads, int kv_heads, int maps, int dim, int vdim, int page_tokens,
+                                             int num_pages, float scale, float lambda, float norm_eps, float out_scale,
+                                             int* status, cudaStream_t stream) {
+  SPROUT_REQUIRE(q && k_cache && v_cache && block_table && q_start && positions && out && status, "multimap_attention_mma: null pointer");
+  SPROUT_REQUIRE(requests > 0 && tiles > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && page_tokens > 0 && num_pages > 0,
+                 "multimap_attention_mma: bad sizes");
+  SPROUT_REQUIRE(mma_sizes(maps, dim, vdim), "multimap_attention_mma: no kernel for %d maps of %d with values of %d", maps, dim, vdim);
+  SPROUT_REQUIRE(q_stride % 8 == 0 && out_stride % 2 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)k_cache & 15) == 0 &&
+                 ((uintptr_t)v_cache & 15) == 0 && ((uintptr_t)out & 3) == 0, "multimap_attention_mma: rows must start on 16-byte boundaries");
+  SPROUT_REQUIRE(kv_heads <= 65535, "multimap_attention_mma: too many key/value heads");
+  MultiMapParams p{(const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
+                   table_stride, q_start, positions, (__nv_bfloat16*)out, out_stride, requests, heads, kv_heads, page_tokens,
+                   num_pages, scale, lambda, norm_eps, out_scale, status};
+#define PICK(D, V)                                                                              \
+  if (dim == D && vdim == V)                                                                    \
+    return maps == 2 ? launch_multimap<D, V, 2>(p, tiles, stream) : launch_multimap<D, V, 1>(p, tiles, stream);
+  PICK(32, 64) PICK(64, 64) PICK(64, 128) PICK(128, 128) PICK(16, 32) PICK(32, 32)
+#undef PICK
+  return sprout_fail("multimap_attention_mma: no kernel for these sizes");
+}
 
 SPROUT_API int sprout_rope_maps_append(void* rows, int row_stride, int dtype, const int* positions, const int* seq_of_token,
                                        const int* block_table, int table_stride, const float* cos_table,

@@ -11,8 +11,15 @@
 //                  output element summed in ascending k by one warp: act = f(W_gate a, W_up a),
 //                  rows = W_down act, f(g, u) = g' sigmoid(alpha g') (u' + 1), g' = min(g, limit),
 //                  u' = clamp(u, -limit, limit).
+//  * moe_up / moe_down (mma):   the same two products on tensor cores (bfloat16, `mma.sync.m16n8k16`, float32
+//                  accumulation): a CTA makes 128 arranged rows of one expert x 128 columns, K in steps of 32
+//                  through a three-stage cp.async ring; the tile list follows the experts' row counts on the
+//                  device.  In the up product a tile holds 64 gate columns and the 64 up columns that go with
+//                  them, so the activation is applied to the accumulators.
 //  * moe_combine:  y[t] += sum over the token's places of weight * (identity ? h[t] : its row).
-#include "common.cuh"
+#include "attention_bf16.cuh"
+
+using namespace sprout_attn;
 
 namespace {
 
@@ -177,6 +184,147 @@ moe_down_plain_kernel(const T* __restrict__ act, const int* __restrict__ offsets
   }
 }
 
+
+// ------------------------------------------------------------------------------------------ tensor cores
+constexpr int GM = 128, GN = 128, GK = 32, GSTRIDE = GK + 8, GSTAGES = 3, GTHREADS = 256;
+constexpr int GEMM_SMEM = GSTAGES * (GM + GN) * GSTRIDE * (int)sizeof(__nv_bfloat16);
+
+// The CTA's tile: expert and first row, from the experts' offsets.  False: no such tile.
+__device__ __forceinline__ bool find_tile(const int* offsets, int experts, int tile, int& expert, int& row0, int& row_end) {
+  for (int e = 0; e < experts; e++) {
+    const int begin = offsets[e], end = offsets[e + 1];
+    const int tiles = (end - begin + GM - 1) / GM;
+    if (tile < tiles) {
+      expert = e;
+      row0 = begin + tile * GM;
+      row_end = end;
+      return true;
+    }
+    tile -= tiles;
+  }
+  return false;
+}
+
+// UP: A rows are h[order[row] / top], B = w[expert] of [2 ff, K] (gate rows, then up rows), out = act [rows, ff] bfloat16.
+// else: A rows are act[row] of [rows, K], B = w[expert] of [N, K], out = rows_out [rows, N] float32.
+template <bool UP>
+__global__ void __launch_bounds__(GTHREADS)
+moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ a, int a_stride, const int* __restrict__ order,
+                    const int* __restrict__ offsets, const __nv_bfloat16* __restrict__ w, void* __restrict__ out,
+                    int experts, int top, int N, int K, float limit, float alpha) {
+  extern __shared__ __align__(16) unsigned char gemm_smem[];
+  typedef __nv_bfloat16 (*Tile)[GSTRIDE];
+  __shared__ const __nv_bfloat16* a_rows[GM];
+  pdl_launch_dependents();
+  pdl_wait();
+  int expert, row0, row_end;
+  if (!find_tile(offsets, experts, blockIdx.x, expert, row0, row_end)) return;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, wm = warp & 3, wn = warp >> 2;
+  const int ff = UP ? N : 0;                         // UP: N is the experts' size, the matrix has 2 N rows
+  const int n0 = blockIdx.y * (UP ? GN / 2 : GN);
+  const __nv_bfloat16* wexp = w + (size_t)expert * (UP ? 2 * N : N) * K;
+  if (tid < GM) {
+    const int row = row0 + tid;
+    a_rows[tid] = row < row_end ? (UP ? a + (size_t)(order[row] / top) * a_stride : a + (size_t)row * a_stride) : nullptr;
+  }
+  __syncthreads();
+  auto As = [&](int stage) { return (Tile)(gemm_smem + (size_t)stage * (GM + GN) * GSTRIDE * sizeof(__nv_bfloat16)); };
+  auto Ws = [&](int stage) { return (Tile)(gemm_smem + ((size_t)stage * (GM + GN) + GM) * GSTRIDE * sizeof(__nv_bfloat16)); };
+  auto load = [&](int stage, int k0) {
+    Tile at = As(stage), wt = Ws(stage);
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+      const int idx = tid + i * GTHREADS, row = idx >> 2, c = (idx & 3) * 8;
+      const bool in_k = k0 + c < K;
+      const __nv_bfloat16* src = a_rows[row];
+      if (src && in_k) cp_async16(&at[row][c], src + k0 + c);
+      else *(uint4*)&at[row][c] = make_uint4(0, 0, 0, 0);
+      int wrow;                                       // the matrix row behind tile row `row`
+      bool in_n;
+      if (UP) {
+        const int j = n0 + (row & 63);
+        in_n = j < ff;
+        wrow = (row < 64 ? 0 : ff) + j;
+      } else {
+        wrow = n0 + row;
+        in_n = wrow < N;
+      }
+      if (in_n && in_k) cp_async16(&wt[row][c], wexp + (size_t)wrow * K + k0 + c);
+      else *(uint4*)&wt[row][c] = make_uint4(0, 0, 0, 0);
+    }
+  };
+  float acc[2][8][4];
+#pragma unroll
+  for (int mi = 0; mi < 2; mi++)
+#pragma unroll
+    for (int ni = 0; ni < 8; ni++) acc[mi][ni][0] = acc[mi][ni][1] = acc[mi][ni][2] = acc[mi][ni][3] = 0.f;
+  const int steps = (K + GK - 1) / GK;
+#pragma unroll
+  for (int s = 0; s < GSTAGES - 1; s++) {
+    if (s < steps) load(s, s * GK);
+    cp_async_commit();
+  }
+  for (int t = 0; t < steps; t++) {
+    cp_async_wait<GSTAGES - 2>();
+    __syncthreads();
+    if (t + GSTAGES - 1 < steps) load((t + GSTAGES - 1) % GSTAGES, (t + GSTAGES - 1) * GK);
+    cp_async_commit();
+    Tile at = As(t % GSTAGES), wt = Ws(t % GSTAGES);
+#pragma unroll
+    for (int kk = 0; kk < GK / 16; kk++) {
+      uint32_t af[2][4];
+#pragma unroll
+      for (int mi = 0; mi < 2; mi++)
+        ldmatrix_x4(af[mi], &at[wm * 32 + mi * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][kk * 16 + (lane >> 4) * 8]);
+#pragma unroll
+      for (int n2 = 0; n2 < 4; n2++) {
+        // UP: the warp's 32 gate columns (tile rows wn * 32 ..) and the 32 up columns that go with them (64 + wn * 32 ..)
+        const int base = UP ? (n2 < 2 ? wn * 32 + n2 * 16 : 64 + wn * 32 + (n2 - 2) * 16) : wn * 64 + n2 * 16;
+        uint32_t b[4];
+        ldmatrix_x4(b, &wt[base + (lane & 7) + (lane >> 4) * 8][kk * 16 + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+        for (int mi = 0; mi < 2; mi++) {
+          mma_bf16(acc[mi][2 * n2], af[mi], b[0], b[1]);
+          mma_bf16(acc[mi][2 * n2 + 1], af[mi], b[2], b[3]);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+  const int gr = lane >> 2, qc = lane & 3;
+#pragma unroll
+  for (int mi = 0; mi < 2; mi++)
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+      const int row = row0 + wm * 32 + mi * 16 + gr + half * 8;
+      if (row >= row_end) continue;
+      if (UP) {
+        __nv_bfloat16* dst = (__nv_bfloat16*)out + (size_t)row * ff;
+#pragma unroll
+        for (int ni = 0; ni < 4; ni++) {
+          const int j = n0 + wn * 32 + ni * 8 + qc * 2;
+          if (j >= ff) continue;
+          float v[2];
+#pragma unroll
+          for (int c = 0; c < 2; c++) {
+            // rounded to bfloat16 before the activation, as separate products would leave them
+            const float g = __bfloat162float(__float2bfloat16_rn(acc[mi][ni][half * 2 + c]));
+            const float u = __bfloat162float(__float2bfloat16_rn(acc[mi][ni + 4][half * 2 + c]));
+            v[c] = glu(g, u, limit, alpha);
+          }
+          *(__nv_bfloat162*)(dst + j) = __floats2bfloat162_rn(v[0], v[1]);
+        }
+      } else {
+        float* dst = (float*)out + (size_t)row * N;
+#pragma unroll
+        for (int ni = 0; ni < 8; ni++) {
+          const int n = n0 + wn * 64 + ni * 8 + qc * 2;
+          if (n < N) *(float2*)(dst + n) = make_float2(acc[mi][ni][half * 2], acc[mi][ni][half * 2 + 1]);
+        }
+      }
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(float* __restrict__ y, const T* __restrict__ h, int h_stride, const int* __restrict__ ids,
@@ -262,6 +410,37 @@ SPROUT_API int sprout_moe_down_plain(const void* act, int dtype, const int* offs
   else
     return sprout_fail("moe_down: unknown dtype %d", dtype);
   return sprout_check_launch("moe_down_plain");
+}
+
+// Whether the tensor-core products take these sizes: rows of 16-byte multiples, pairs of outputs.
+SPROUT_API int sprout_moe_mma_supported(int width, int ff, int h_stride) {
+  return width % 8 == 0 && ff % 8 == 0 && h_stride % 8 == 0;
+}
+
+// act [entries, ff] bfloat16 = glu(W_gate a, W_up a); rows_out [entries, width] float32 = W_down act, over the arranged rows.
+SPROUT_API int sprout_moe_experts_mma(const void* h, int h_stride, const int* order, const int* offsets, const void* w_gate_up,
+                                      const void* w_down, void* act, float* rows_out, int entries, int experts, int top,
+                                      int width, int ff, float limit, float alpha, cudaStream_t stream) {
+  SPROUT_REQUIRE(h && order && offsets && w_gate_up && w_down && act && rows_out, "moe_experts_mma: null pointer");
+  SPROUT_REQUIRE(entries > 0 && experts > 0 && top > 0 && sprout_moe_mma_supported(width, ff, h_stride),
+                 "moe_experts_mma: sizes must be multiples of 8 (width %d, ff %d, row stride %d)", width, ff, h_stride);
+  SPROUT_REQUIRE((((uintptr_t)h | (uintptr_t)w_gate_up | (uintptr_t)w_down | (uintptr_t)act | (uintptr_t)rows_out) & 15) == 0,
+                 "moe_experts_mma: buffers must start on 16-byte boundaries");
+  static bool prepared = false;
+  if (!prepared) {
+    cudaFuncSetAttribute(moe_gemm_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    cudaFuncSetAttribute(moe_gemm_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    prepared = true;
+  }
+  const int tiles = (entries + GM - 1) / GM + experts;       // at most this many row tiles, whatever the routing
+  sprout_launch(moe_gemm_mma_kernel<true>, dim3(tiles, (ff + GN / 2 - 1) / (GN / 2)), dim3(GTHREADS), GEMM_SMEM, stream,
+                (const __nv_bfloat16*)h, h_stride, order, offsets, (const __nv_bfloat16*)w_gate_up, act, experts, top, ff, width,
+                limit, alpha);
+  if (int code = sprout_check_launch("moe_up_mma")) return code;
+  sprout_launch(moe_gemm_mma_kernel<false>, dim3(tiles, (width + GN - 1) / GN), dim3(GTHREADS), GEMM_SMEM, stream,
+                (const __nv_bfloat16*)act, ff, order, offsets, (const __nv_bfloat16*)w_down, (void*)rows_out, experts, top, width, ff,
+                0.f, 0.f);
+  return sprout_check_launch("moe_down_mma");
 }
 
 SPROUT_API int sprout_moe_combine(float* y, const void* h, int h_stride, int dtype, const int* ids, const float* weights,

@@ -69,12 +69,16 @@ _SIGNATURES = {
     "sprout_glu_clamped": [_P, _P, _I, _I, _I, _F, _F, _P],
     "sprout_rope_maps_append": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_multimap_attention_simple": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _P, _P],
+    "sprout_multimap_attention_mma": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _P, _P],
+    "sprout_multimap_attention_mma_supported": [_I, _I, _I],
     "sprout_decay_scan": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "sprout_moe_route": [_P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
     "sprout_moe_arrange": [_P, _P, _P, _P, _P, _I, _I, _P],
     "sprout_moe_up_plain": [_P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _P],
     "sprout_moe_down_plain": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
     "sprout_moe_combine": [_P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _P],
+    "sprout_moe_mma_supported": [_I, _I, _I],
+    "sprout_moe_experts_mma": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _P],
 }
 
 _lock = threading.Lock()
@@ -1264,7 +1268,27 @@ def moe_combine(y, h, ids, weights, place_of, rows, top: int):
 
 def multimap_attention(q, cache, ctx, out, heads: int, kv_heads: int, maps: int, dim: int, vdim: int, scale: float, lam: float,
                        norm_eps: float, out_scale: float, status):
-    """Attention with one or two maps per head: picks the kernel for the dtype and the sizes."""
+    """Attention with one or two maps per head: the tensor-core kernel in bfloat16 for the sizes it is built for
+    (``SPROUT_MULTIMAP_ATTENTION=simple`` keeps the float32-arithmetic kernel), else the float32-arithmetic kernel."""
+    if q.dtype == torch.bfloat16 and os.environ.get("SPROUT_MULTIMAP_ATTENTION", "mma") != "simple" \
+            and (_lib or load_library()).sprout_multimap_attention_mma_supported(maps, dim, vdim) \
+            and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.stride(0) % 2 == 0:
+        _rows_contiguous(q, "q")
+        _rows_contiguous(out, "out")
+        k_cache, v_cache = cache.k, cache.v
+        if tuple(k_cache.shape[1:]) != (kv_heads, cache.page_tokens, maps * dim) or tuple(v_cache.shape[1:]) != (kv_heads, cache.page_tokens, vdim) \
+                or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype or out.dtype != q.dtype:
+            raise KernelError("multimap_attention: the cache's shape or dtype does not fit the heads")
+        if q.shape[1] != heads * maps * dim or out.shape[1] != heads * vdim or out.shape[0] != q.shape[0]:
+            raise KernelError("multimap_attention: q or out has the wrong width")
+        requests = ctx.q_start.numel() - 1
+        tiles = (q.shape[0] * (heads // kv_heads) + 63) // 64 + requests
+        _run("sprout_multimap_attention_mma", _ptr(q, "q"), q.stride(0), _ptr(k_cache, "k_cache"), _ptr(v_cache, "v_cache"),
+             _ptr(cache.block_table, "block_table", torch.int32), cache.block_table.stride(0),
+             _ptr(ctx.q_start, "q_start", torch.int32), _ptr(ctx.positions, "positions", torch.int32), _ptr(out, "out"),
+             out.stride(0), requests, tiles, heads, kv_heads, maps, dim, vdim, cache.page_tokens, k_cache.shape[0], float(scale),
+             float(lam), float(norm_eps), float(out_scale), _ptr(status, "status", torch.int32), _stream())
+        return
     multimap_attention_simple(q, cache, ctx, out, heads, kv_heads, maps, dim, vdim, scale, lam, norm_eps, out_scale, status)
 
 
@@ -1274,7 +1298,19 @@ def decay_attention(rows, ctx, state, decay, out, heads: int, dim: int, vdim: in
 
 
 def moe_experts(h, order, offsets, w_gate_up, w_down, act, rows_out, experts: int, top: int, limit: float, alpha: float):
-    """The routed experts' two products over the arranged rows."""
+    """The routed experts' two products over the arranged rows: on tensor cores in bfloat16 when the sizes are
+    multiples of 8 (``SPROUT_MOE=plain`` keeps the CUDA-core products), else on CUDA cores."""
+    global LAUNCHES
+    width, ff = h.shape[1], act.shape[1]
+    if h.dtype == torch.bfloat16 and h.stride(1) == 1 and os.environ.get("SPROUT_MOE", "mma") != "plain" \
+            and (_lib or load_library()).sprout_moe_mma_supported(width, ff, h.stride(0)) \
+            and all(t.data_ptr() % 16 == 0 for t in (h, w_gate_up, w_down, act, rows_out)):
+        _run("sprout_moe_experts_mma", _ptr(h, "h"), h.stride(0), _ptr(order, "order", torch.int32),
+             _ptr(offsets, "offsets", torch.int32), _ptr(w_gate_up, "w_gate_up", torch.bfloat16),
+             _ptr(w_down, "w_down", torch.bfloat16), _ptr(act, "act", torch.bfloat16), _ptr(rows_out, "rows_out", torch.float32),
+             act.shape[0], experts, top, width, ff, float(limit), float(alpha), _stream())
+        LAUNCHES += 1               # two kernels behind one call
+        return
     moe_up_plain(h, order, offsets, w_gate_up, act, experts, top, limit, alpha)
     moe_down_plain(act, offsets, w_down, rows_out, experts)
 

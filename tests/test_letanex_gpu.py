@@ -112,7 +112,8 @@ def _fill_cache(kernels, dtype, contexts, G, maps, dim, vdim, page, cos, sin, rn
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("sizes", [(6, 2, 16, 24, 8, 16), (3, 3, 8, 8, 4, 8), (2, 1, 12, 40, 12, 16), (4, 2, 32, 64, 16, 16)])
+@pytest.mark.parametrize("sizes", [(6, 2, 16, 24, 8, 16), (3, 3, 8, 8, 4, 8), (2, 1, 12, 40, 12, 16), (4, 2, 32, 64, 16, 16),
+                                   (8, 2, 64, 128, 32, 16), (3, 1, 16, 32, 8, 8), (2, 2, 128, 128, 64, 32)])
 def test_two_map_attention_over_pages(dtype, sizes):
     """Rotation, append and attention together: contexts on both sides of page and 128-key borders, a portion of
     queries and single queries, pages in shuffled order."""
@@ -136,7 +137,8 @@ def test_two_map_attention_over_pages(dtype, sizes):
     rows = dev(q.reshape(len(positions), -1), dtype)
     kernels.rope_maps_append(rows, ints(positions), ints(seqs), view.block_table, cos, sin, None, None, H * 2, G, 2, dim, vdim,
                              page, False, status)
-    ctx = SimpleNamespace(positions=ints(positions), seq_of_token=ints(seqs))
+    starts = np.concatenate([[0], np.cumsum([min(n, 5) for n in contexts])])
+    ctx = SimpleNamespace(positions=ints(positions), seq_of_token=ints(seqs), q_start=ints(starts))
     out = torch.empty(len(positions), H * vdim, dtype=DTYPES[dtype], device=DEV)
     kernels.multimap_attention(rows, view, ctx, out, H, G, 2, dim, vdim, scale, lam, eps, out_scale, status)
     got = out.float().cpu().numpy().reshape(len(positions), H, vdim)
@@ -153,11 +155,12 @@ def test_two_map_attention_over_pages(dtype, sizes):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_attention_finds_a_far_key_and_ignores_the_future(dtype):
+@pytest.mark.parametrize("dims", [(16, 24), (32, 64)])
+def test_attention_finds_a_far_key_and_ignores_the_future(dtype, dims):
     """One key among 700, far back, is the only one map 0 of one head scores high: the head's output must be that
     key's value.  A huge key one position after the query must not be seen.  With one map, the plain softmax."""
     from sprout_lm_b200 import kernels
-    H, G, dim, vdim, page, n = 2, 1, 16, 24, 16, 700
+    (dim, vdim), H, G, page, n = dims, 2, 1, 16, 700
     rng = np.random.default_rng(9)
     keys = rng.normal(0, 0.1, size=(n, G, 2, dim))
     values = rng.normal(0, 1.0, size=(n, G, vdim))
@@ -168,7 +171,7 @@ def test_attention_finds_a_far_key_and_ignores_the_future(dtype):
     view, k, v, status = _fill_cache(kernels, dtype, [n], G, 2, dim, vdim, page, None, None, rng, keys=[keys], values=[values])
     q = np.zeros((1, H, 2, dim))
     q[0, 0, 0, 5] = 8.0                            # head 0, map 0 asks for the far key; the other maps are uniform
-    ctx = SimpleNamespace(positions=ints([query_at]), seq_of_token=ints([0]))
+    ctx = SimpleNamespace(positions=ints([query_at]), seq_of_token=ints([0]), q_start=ints([0, 1]))
     out = torch.empty(1, H * vdim, dtype=DTYPES[dtype], device=DEV)
     kernels.multimap_attention(dev(q.reshape(1, -1).astype(np.float32), dtype), view, ctx, out, H, G, 2, dim, vdim, 1.0, 0.0, 0.0, 1.0, status)
     got = out.float().cpu().numpy().reshape(H, vdim)
@@ -251,7 +254,8 @@ def test_decay_scan_carries_state(dtype, sizes):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("sizes", [(5, 2, 2, 24, 1.0, True), (3, 0, 1, 16, 0.5, False), (4, 3, 5, 8, 2.5, True), (8, 4, 3, 40, 1.5, False)])
+@pytest.mark.parametrize("sizes", [(5, 2, 2, 24, 1.0, True), (3, 0, 1, 16, 0.5, False), (4, 3, 5, 8, 2.5, True), (8, 4, 3, 40, 1.5, False),
+                                   (6, 1, 3, 12, 1.2, True), (3, 2, 2, 200, 1.0, False)])
 def test_routed_experts_part(dtype, sizes):
     """The whole routed feed-forward against the oracle: choice by score + correction, weights without it, identity
     experts, a single expert per token, nearly all experts per token, with and without a shared expert."""
