@@ -1,6 +1,6 @@
 """Tiny Letanex configurations and model folders for the tests.
 
-The two configurations differ in every size and constant and avoid choices that would hide a mix-up: query/key
+The first two configurations differ in every size and constant and avoid choices that would hide a mix-up: query/key
 and value sizes of a head differ in one and are equal in the other, one has as many key/value heads as heads, the
 rotated width is smaller than a map's vectors, one rotation has no scaling, one decay is exactly 1, one router takes
 a single expert and another nearly all, one mixture has no identity experts and one no shared expert, one layer has
@@ -60,7 +60,17 @@ Q = {"architecture": "Letanex", "vocab": 255, "width": 64, "norm": {"eps": 1e-6}
          layer(lightning(2, 16, 16, (0.7, 0.95)), dense(48)),
          layer(attention(6, 3, 8, 8, 0.5, 0.45, 10000.0, 4, factor=1.5, kv_from=0), moe(6, 2, 3, 1.0, 16, 1.0)),
      ]}
-CONFIGS = {"P": (P, 3, 16), "Q": (Q, 4, 8)}            # name -> (config.json, seed, page size)
+# sizes that the tensor-core kernels of the bfloat16 path are built for (key vectors of 16 and 64 with values of 32 and 64,
+# a recurrent state with keys of 64, experts in multiples of 8)
+R = {"architecture": "Letanex", "vocab": 277, "width": 96, "norm": {"eps": 1e-5},
+     "layers": [
+         layer(lightning(2, 64, 32, (0.9, 0.99)), moe(6, 1, 2, 1.2, 32, 1.5, shared=(48, 2.0))),
+         layer(attention(4, 1, 16, 32, 0.35, 0.4, 2000.0, 8, factor=2.0), dense(160)),
+         layer(attention(2, 1, 16, 32, 0.3, 0.7, 2000.0, 8, factor=2.0, kv_from=1), moe(4, 0, 2, 1.0, 64, 1.0)),
+         layer(attention(2, 2, 64, 64, 0.2, 0.5, 50000.0, 64), None),
+     ]}
+CONFIGS = {"P": (P, 3, 16), "Q": (Q, 4, 8), "R": (R, 5, 16)}            # name -> (config.json, seed, page size)
+MIXER_SCALE = {"P": 3.0, "Q": 3.0, "R": 1.5}       # R's long key vectors make sharp scores already
 
 
 def make_model_dir(base, name: str) -> Path:
@@ -81,7 +91,7 @@ def make_model_dir(base, name: str) -> Path:
         for key in handle.names():
             value = handle.tensor(key).float()
             if ".mix." in key and value.dim() == 2:
-                value = value * 3.0
+                value = value * MIXER_SCALE[name]
             elif key.endswith(".router"):
                 value = value * 100.0               # decisive scores: few nearly tied choices for bfloat16 to fall either way
             elif key.endswith(".correction"):
@@ -118,10 +128,12 @@ def plain_logits(directory, tokens) -> np.ndarray:
 def compare(directory, requests: dict, got: dict, tol: float, label: str, page: int, outliers: float = 0.0):
     """Every place that came back against the oracle, by the root mean square of the difference over the vocabulary
     (the logits' own root mean square is near one); a failure names the first wrong token and its place.
-    ``outliers``: the share of places that may lie over the bar.  In bfloat16 the models' sharp choices (a router's
-    nearly tied scores, a softmax over large scores) sometimes fall the other way: the median difference is well under
-    a hundredth, and a few places in a hundred lie many times above it; a fault of the cache, the state or a kernel
-    moves most places (the median must stay under half the bar).  In 32-bit no place may differ."""
+    ``outliers``: the share of places that may lie over the bar.  In 32-bit no place may differ.  In bfloat16 a
+    router's nearly tied choice sometimes falls the other way (some ten times among these requests' tokens), and what
+    that changes stays in the recurrent state and the cached values of the request's later tokens; so there the bar
+    holds for the median (at half its height) and for three quarters of the places, which a fault of a kernel's
+    indexing or dispatch would move, while keys at borders, far keys and carried state are held to tight bars in
+    bfloat16 by the mechanisms' own tests, where nothing is routed."""
     assert got, "no logits came back"
     errors, first = [], None
     for rid, tokens in requests.items():

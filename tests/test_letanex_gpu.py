@@ -189,7 +189,8 @@ def test_attention_finds_a_far_key_and_ignores_the_future(dtype, dims):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("sizes", [(3, 8, 20, (0.9, 0.5, 0.99)), (1, 24, 8, (1.0,)), (2, 32, 64, (0.6, 0.999)), (2, 16, 130, (0.8, 0.97))])
+@pytest.mark.parametrize("sizes", [(3, 8, 20, (0.9, 0.5, 0.99)), (1, 24, 8, (1.0,)), (2, 32, 64, (0.6, 0.999)), (2, 16, 130, (0.8, 0.97)),
+                                   (2, 64, 40, (0.95, 1.0)), (1, 128, 64, (0.999,)), (3, 64, 128, (0.5, 0.9, 0.99))])
 def test_decay_scan_carries_state(dtype, sizes):
     """Whole against portions against token by token; slots given back and used again; a decay of exactly 1."""
     from sprout_lm_b200 import kernels
@@ -201,7 +202,9 @@ def test_decay_scan_carries_state(dtype, sizes):
     state = torch.full((3, heads, dim, vdim), float("nan"), device=DEV)
     decay_t = dev(np.asarray(decay, dtype=np.float32))
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    tol = 2e-4 if dtype == "float32" else 5e-2
+    # token by token everything is float32 on inputs the rows' type holds exactly; 64 tokens at a time the decayed
+    # scores are rounded to bfloat16 for the value product (the portions of 8 tokens and more of bfloat16 rows)
+    tol = 1e-2 if dtype == "bfloat16" and dim in (64, 128) else 2e-4
 
     def activated(rows):
         act = plain.silu(rows.numpy().astype(np.float64))
@@ -220,7 +223,7 @@ def test_decay_scan_carries_state(dtype, sizes):
         rows = torch.cat([r for _, r in batch])
         starts = np.concatenate([[0], np.cumsum([r.shape[0] for _, r in batch])])
         out = torch.empty(rows.shape[0], heads * vdim, device=DEV)
-        ctx = SimpleNamespace(q_start=ints(starts))
+        ctx = SimpleNamespace(q_start=ints(starts), max_q_len=max(r.shape[0] for _, r in batch))
         view = SimpleNamespace(buffer=state, slots=ints([s for s, _ in batch]))
         kernels.decay_attention(dev(rows, dtype), ctx, view, decay_t, out, heads, dim, vdim, True, status)
         got = out.cpu().numpy()
@@ -346,7 +349,7 @@ def test_layers_one_by_one(model_dirs):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["P", "Q"])
+@pytest.mark.parametrize("name", ["P", "Q", "R"])
 def test_all_cuttings_in_process(model_dirs, name, dtype):
     """Whole, tail decoded token by token (80 tokens), portions down to two tokens, mixed batches with pages and
     state slots used again: against the plain implementation, and in 32-bit bitwise equal to one another."""
@@ -365,7 +368,7 @@ def test_all_cuttings_in_process(model_dirs, name, dtype):
         runner = make_runner(model_dirs[name], dtype, budget // page, page, requests=4)
         got = results[label] = helpers.run_plan_in_process(runner, plan)
         assert len(got) == sum(len(t) for t in requests.values())
-        worst = lh.compare(model_dirs[name], requests, got, TOL[dtype], f"{name}/{dtype}/{label}", page, outliers=0.05 if dtype == "bfloat16" else 0.0)
+        worst = lh.compare(model_dirs[name], requests, got, TOL[dtype], f"{name}/{dtype}/{label}", page, outliers=0.25 if dtype == "bfloat16" else 0.0)
         print(f"{name}/{dtype}/{label}: worst difference {worst:.2e}")
         runner.manager.check_invariants()
         assert len(runner.manager.pools[0].free) == runner.manager.pools[0].num_pages        # every page came back
@@ -385,7 +388,7 @@ def test_long_context_crosses_many_pages(model_dirs):
     for dtype in ("float32", "bfloat16"):
         runner = make_runner(model_dirs[name], dtype, 70, 8)
         got = helpers.run_plan_in_process(runner, plan)
-        lh.compare(model_dirs[name], requests, got, TOL[dtype], f"long/{dtype}", 8, outliers=0.05 if dtype == "bfloat16" else 0.0)
+        lh.compare(model_dirs[name], requests, got, TOL[dtype], f"long/{dtype}", 8, outliers=0.25 if dtype == "bfloat16" else 0.0)
 
 
 def test_a_lost_state_or_wrong_slot_shows(model_dirs):
@@ -407,7 +410,7 @@ def test_trace_replay_program(model_dirs, tmp_path):
     vocab = lh.CONFIGS[name][0]["vocab"]
     for dtype in ("float32", "bfloat16"):
         got = helpers.run_plan_with_trace_run(model_dirs[name], dtype, plan, tmp_path / dtype, budget, vocab=vocab)
-        lh.compare(model_dirs[name], requests, got, TOL[dtype], f"trace/{dtype}", 16, outliers=0.05 if dtype == "bfloat16" else 0.0)
+        lh.compare(model_dirs[name], requests, got, TOL[dtype], f"trace/{dtype}", 16, outliers=0.25 if dtype == "bfloat16" else 0.0)
 
 
 @pytest.mark.parametrize("name", ["P", "Q"])
