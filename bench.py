@@ -809,6 +809,192 @@ def timed_latent(args) -> dict:
     return result
 
 
+# Letanex (differential attention, linear attention with decay and state, routed experts) at sizes that resemble a real
+# model's layers, and the Qwen2 configuration of equal width, heads, layers, vocabulary and active feed-forward
+# parameters beside it (grouped-query attention with heads of 128, SwiGLU)
+LETANEX_SHAPES = {
+    "1b": dict(width=2048, heads=16, kv_heads=4, dim=64, vdim=128, state_heads=16, state_dim=128, ff=8192, experts=32,
+               identity=4, top=4, expert_ff=1024, shared_ff=2048, vocab=32768, qwen=dict(intermediate_size=6144, num_key_value_heads=4)),
+    "0.3b": dict(width=1024, heads=8, kv_heads=2, dim=64, vdim=128, state_heads=8, state_dim=128, ff=4096, experts=16,
+                 identity=2, top=4, expert_ff=512, shared_ff=1024, vocab=32768, qwen=dict(intermediate_size=3072, num_key_value_heads=2)),
+}
+
+
+def letanex_folders(shape: str, layers: int):
+    """(Letanex folder, Qwen2 folder of equal size), random weights, written once.  Layers in fours: attention with a dense
+    feed-forward, attention over the first one's keys and values with routed experts, two layers of linear attention with
+    routed experts."""
+    from sprout_lm_b200 import parse_config, write_random_model
+    z = LETANEX_SHAPES[shape]
+    moe = {"kind": "moe", "router": {"experts": z["experts"], "identity": z["identity"], "top": z["top"], "scale": 1.0},
+           "expert": {"ff": z["expert_ff"], "limit": 7.0}, "shared": {"ff": z["shared_ff"], "limit": 7.0}}
+    entries = []
+    for i in range(layers):
+        if i % 4 < 2:
+            mixer = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+                     "diff": 0.5, "rot": {"base": 10000.0, "dims": z["dim"], "scaling": {"factor": 8.0}}}
+            if i % 4 == 1:
+                mixer["kv_from"] = i - 1
+            entries.append({"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": z["ff"]} if i % 4 == 0 else moe})
+        else:
+            decay = [float(1.0 - 2.0 ** (-5 - 3 * h / max(1, z["state_heads"] - 1))) for h in range(z["state_heads"])]
+            entries.append({"type": "lightning", "mlp": moe,
+                            "mixer": {"heads": z["state_heads"], "dim": z["state_dim"], "vdim": z["vdim"], "decay": decay}})
+    raw = {"architecture": "Letanex", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "layers": entries,
+           "max_positions": 16384}
+    qwen = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_act": "silu", "hidden_size": z["width"],
+            "num_hidden_layers": layers, "num_attention_heads": z["heads"], "vocab_size": z["vocab"],
+            "max_position_embeddings": 16384, "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "tie_word_embeddings": False,
+            "eos_token_id": 0, **z["qwen"]}
+    folders = []
+    for tag, config in (("letanex", raw), ("qwen2", qwen)):
+        folder = Path(tempfile.gettempdir()) / f"sprout_lm_b200_bench_{os.getuid()}_letanex_{shape}_{tag}_L{layers}"
+        if not (folder / "complete").exists():
+            print(f"[bench] writing random weights to {folder}", file=sys.stderr, flush=True)
+            write_random_model(folder, parse_config(config), seed=0)
+            (folder / "complete").write_text("ok")
+        folders.append(folder)
+    return folders[0], folders[1], raw, qwen
+
+
+def timed_letanex_kernels(shape: str, tokens: int, batch: int, context: int, peak: dict) -> dict:
+    """The new design's kernels alone beside the closest kernels of the grouped-query model at equal sizes: attention over
+    one prompt of ``tokens`` tokens (executed FLOPs of the causal half against the measured bf16 rate) and ``batch`` single
+    tokens over ``context`` keys each (cache bytes against the measured copy rate); the linear attention's prompt kernel
+    (bytes it must move against the copy rate; its FLOPs are small); the routed experts' two products beside the dense
+    SwiGLU products of as many FLOPs."""
+    import torch
+    from types import SimpleNamespace
+    from sprout_lm_b200 import kernels
+    from sprout_lm_b200.parts.linear import Linear
+    z = LETANEX_SHAPES[shape]
+    heads, kv, dim, vdim, page = z["heads"], z["kv_heads"], z["dim"], z["vdim"], 16
+    g = torch.Generator(device="cuda").manual_seed(0)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = {}
+
+    def rand(*shape_, scale=1.0):
+        return (torch.randn(*shape_, device="cuda", generator=g) * scale).to(torch.bfloat16)
+
+    def ctx_for(requests, new, held):
+        return SimpleNamespace(seq_of_token=torch.arange(requests, dtype=torch.int32, device="cuda").repeat_interleave(new),
+                               positions=(torch.arange(new, dtype=torch.int32, device="cuda") + (held - new)).repeat(requests),
+                               q_start=(torch.arange(requests + 1, dtype=torch.int32, device="cuda") * new),
+                               context_lens=torch.full((requests,), held, dtype=torch.int32, device="cuda"), max_q_len=new,
+                               max_context=held, planned_context=0, num_seqs=requests, num_tokens=requests * new)
+    gqa_dim = 2 * dim                                   # the grouped-query model's head size: as many query/key elements per head
+    for label, requests, new, held in (("prefill", 1, tokens, tokens), ("decode", batch, 1, context)):
+        pages = -(-held // page)
+        width_t = -(-pages // 64) * 64
+        table = torch.full((requests, width_t), -1, dtype=torch.int32, device="cuda")
+        table[:, :pages] = torch.randperm(requests * pages, device="cuda", generator=g).to(torch.int32).reshape(requests, pages)
+        ctx = ctx_for(requests, new, held)
+        k2, v2 = rand(requests * pages + 1, kv, page, 2 * dim), rand(requests * pages + 1, kv, page, vdim)
+        q2 = rand(requests * new, heads * 2 * dim, scale=0.3)
+        o2 = torch.empty(requests * new, heads * vdim, dtype=torch.bfloat16, device="cuda")
+        view = SimpleNamespace(k=k2, v=v2, block_table=table, page_tokens=page, write=False)
+        us = _median_us(lambda: kernels.multimap_attention(q2, view, ctx, o2, heads, kv, 2, dim, vdim, dim ** -0.5, 0.4, 1e-5, 0.5, status),
+                        repeats=3 if label == "prefill" else 10)
+        kg, vg = rand(requests * pages + 1, kv, page, gqa_dim), rand(requests * pages + 1, kv, page, gqa_dim)
+        qg = rand(requests * new, heads * gqa_dim, scale=0.3)
+        og = torch.empty_like(qg)
+        if label == "prefill":
+            flops = 4.0 * heads * (dim + vdim) * tokens * (tokens + 1) / 2
+            out["two_map_prefill"] = {"us": round(us, 1), "tflops": round(flops / us / 1e6, 1),
+                                      "of_measured_bf16": round(flops / us / 1e6 / peak["bf16_tflops"], 3)}
+            variant = "tcgen05" if gqa_dim in (64, 128) else "mma_sync"
+            for name, var in (("gqa_prefill", variant), ("gqa_prefill_mma_sync", "mma_sync")):
+                us = _median_us(lambda: kernels.attention_prefill(qg, kg, vg, table, ctx.q_start, ctx.positions, og, heads, kv, gqa_dim,
+                                                                  status, variant=var), repeats=3)
+                flops = 4.0 * heads * gqa_dim * tokens * (tokens + 1) / 2
+                out[name] = {"us": round(us, 1), "tflops": round(flops / us / 1e6, 1), "variant": var,
+                             "of_measured_bf16": round(flops / us / 1e6 / peak["bf16_tflops"], 3)}
+        else:
+            mb = batch * context * kv * (2 * dim + vdim) * 2 / 1e6
+            out["two_map_decode"] = {"us": round(us, 1), "gbs": round(mb / us * 1e3), "mb": round(mb, 1),
+                                     "of_measured_copy": round(mb / us * 1e3 / peak["hbm_gbs"], 3)}
+            us = _median_us(lambda: kernels.attention_decode(qg, kg, vg, table, ctx.context_lens, og, heads, kv, gqa_dim, status,
+                                                             live_keys=-(-context // 128) * 128))
+            mb = 2.0 * batch * context * kv * gqa_dim * 2 / 1e6
+            out["gqa_decode"] = {"us": round(us, 1), "gbs": round(mb / us * 1e3), "mb": round(mb, 1),
+                                 "of_measured_copy": round(mb / us * 1e3 / peak["hbm_gbs"], 3)}
+    # linear attention with decay: a prompt, and single tokens
+    sh, sd = z["state_heads"], z["state_dim"]
+    decay = torch.full((sh,), 0.99, device="cuda")
+    for label, requests, new in (("prefill", 1, tokens), ("decode", batch, 1)):
+        rows = rand(requests * new, sh * (2 * sd + 2 * vdim), scale=0.5)
+        state = torch.zeros(requests, sh, sd, vdim, device="cuda")
+        view = SimpleNamespace(buffer=state, slots=torch.arange(requests, dtype=torch.int32, device="cuda"))
+        o = torch.empty(requests * new, sh * vdim, device="cuda")
+        ctx = ctx_for(requests, new, new)
+        us = _median_us(lambda: kernels.decay_attention(rows, ctx, view, decay, o, sh, sd, vdim, True, status), repeats=3 if new > 1 else 10)
+        mb = (requests * new * sh * ((2 * sd + vdim) * 2 + vdim * 4) + 2 * requests * sh * sd * vdim * 4) / 1e6
+        out[f"decay_{label}"] = {"us": round(us, 1), "mb": round(mb, 1), "gbs": round(mb / us * 1e3),
+                                 "of_measured_copy": round(mb / us * 1e3 / peak["hbm_gbs"], 3),
+                                 "tflops": round(4.0 * requests * new * sh * sd * vdim / us / 1e6, 2)}
+    # routed experts beside dense products of as many FLOPs
+    W, E, top, ff = z["width"], z["experts"], z["top"], z["expert_ff"]
+    w_gu, w_d = rand(E, 2 * ff, W, scale=0.02), rand(E, W, ff, scale=0.02)
+    dense_gu = Linear(rand(2 * top * ff, W, scale=0.02), None, status)
+    dense_d = Linear(rand(W, top * ff, scale=0.02), None, status)
+    for label, n in (("prefill", tokens), ("decode", batch)):
+        h = rand(n, W)
+        ids = torch.stack([torch.randperm(E, device="cuda", generator=g)[:top] for _ in range(n)]).to(torch.int32).contiguous()
+        counts = torch.bincount(ids.flatten().long(), minlength=E).to(torch.int32)
+        offsets = torch.zeros(E + 1, dtype=torch.int32, device="cuda")
+        order, place_of = torch.empty(n * top, dtype=torch.int32, device="cuda"), torch.empty(n * top, dtype=torch.int32, device="cuda")
+        kernels.moe_arrange(ids, counts, offsets, order, place_of, E)
+        act = torch.empty(n * top, ff, dtype=torch.bfloat16, device="cuda")
+        rows_out = torch.empty(n * top, W, device="cuda")
+        us = _median_us(lambda: kernels.moe_experts(h, order, offsets, w_gu, w_d, act, rows_out, E, top, 7.0, 1.702), repeats=3 if n > 256 else 10)
+        flops = 6.0 * n * top * W * ff
+        mb = (w_gu.numel() + w_d.numel()) * 2 / 1e6
+        out[f"experts_{label}"] = {"us": round(us, 1), "tflops": round(flops / us / 1e6, 1), "of_measured_bf16": round(flops / us / 1e6 / peak["bf16_tflops"], 3),
+                                   "weights_gbs": round(mb / us * 1e3), "weights_of_measured_copy": round(mb / us * 1e3 / peak["hbm_gbs"], 3)}
+        x = torch.zeros(n, W, device="cuda")
+
+        def dense():
+            dense_d.forward(dense_gu.forward_swiglu(h, 8), residual=x)
+        us = _median_us(dense, repeats=3 if n > 256 else 10)
+        mb = (dense_gu.weight.numel() + dense_d.weight.numel()) * 2 / 1e6
+        out[f"dense_swiglu_{label}"] = {"us": round(us, 1), "tflops": round(flops / us / 1e6, 1), "of_measured_bf16": round(flops / us / 1e6 / peak["bf16_tflops"], 3),
+                                        "weights_gbs": round(mb / us * 1e3), "weights_of_measured_copy": round(mb / us * 1e3 / peak["hbm_gbs"], 3)}
+    assert int(status.item()) == 0
+    return out
+
+
+def timed_letanex(args) -> dict:
+    """``--only letanex``: prefill and decode throughput of Letanex at ``--shape 1b|0.3b`` (random weights, ``--layers``
+    layers, 4 if not given) beside Qwen2 at equal size, through the same runner, and the kernels of both alone."""
+    import numpy as np
+    import torch
+    from sprout_lm_b200 import load_model
+    from sprout_lm_b200.engine.step import ModelRunner
+    shape = args.shape if args.shape in LETANEX_SHAPES else "1b"
+    layers = args.layers or 4
+    peak = peaks()
+    letanex_dir, qwen_dir, _, _ = letanex_folders(shape, layers)
+    prompt_len = args.prompt_len
+    result = {"impl": "ours", "only": "letanex", "shape": shape, "layers": layers, "dtype": "bf16", "data": "synthetic",
+              "prefill_tokens": args.tokens, "decode_batch": args.batch, "decode_prompt_len": prompt_len, "steps": args.steps,
+              "peaks": {"bf16_tflops": peak["bf16_tflops"], "hbm_gbs": peak["hbm_gbs"], "source": peak.get("source", "measured")}}
+    for tag, folder in (("letanex", letanex_dir), ("qwen2", qwen_dir)):
+        model = load_model(folder, dtype="bfloat16", device="cuda:0")
+        slots = max(64, args.batch)
+        pages = slots * (-(-(prompt_len + args.steps + args.warmup + 16) // 16)) + args.tokens // 16 + 16
+        runner = ModelRunner(model, num_pages=pages, page_tokens=16, max_requests=slots, prefix_caching=False)
+        rng = np.random.default_rng(0)
+        ms = timed_prefill(runner, args.tokens, rng)
+        decode = timed_decode(runner, args.batch, prompt_len, args.steps, args.warmup, rng)
+        result[tag] = {"prefill_ms": round(ms, 3), "prefill_tokens_per_s": round(args.tokens / ms * 1000),
+                       "decode_ms_per_step": round(decode["ms_per_step"], 4), "decode_tokens_per_s": round(decode["tokens_per_s"]),
+                       "decode_launches_per_step": decode["launches_per_step"]}
+        del runner, model
+        torch.cuda.empty_cache()
+    result["kernels"] = timed_letanex_kernels(shape, args.tokens, max(args.batch, 64), 2048, peak)
+    return result
+
+
 def run(args) -> dict:
     import numpy as np
     import torch
@@ -818,6 +1004,8 @@ def run(args) -> dict:
     kernels.load_library(verbose=True)
     if args.only == "latent":
         return timed_latent(args)
+    if args.only == "letanex":
+        return timed_letanex(args)
     if args.only == "attention":
         return timed_attention(args.tokens, args.shape)
     if args.only == "gemm":
@@ -925,7 +1113,7 @@ def main() -> int:
     parser.add_argument("--portion", type=int, default=4096, help="with --only long-prompt: tokens of a step (--tokens: of the whole prompt)")
     parser.add_argument("--prompt-len", type=int, default=512, help="with --only decode: tokens of every request's prompt (the context grows to hold it)")
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
-    parser.add_argument("--only", choices=["all", "decode", "prefill", "ablate", "attention", "decode-attention", "gemm", "serve", "long-prompt", "latent"], default="all",
+    parser.add_argument("--only", choices=["all", "decode", "prefill", "ablate", "attention", "decode-attention", "gemm", "serve", "long-prompt", "latent", "letanex"], default="all",
                         help="measure one part only (for profiling captures); the JSON line then holds that part")
     parser.add_argument("--shape", choices=sorted(SHAPES) + sorted(LATENT_SHAPES), default="0.5b", help="with --only: the model's sizes")
     parser.add_argument("--requests", type=int, default=64, help="with --only serve: requests of the workload")

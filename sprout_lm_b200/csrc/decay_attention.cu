@@ -79,31 +79,44 @@ decay_scan_kernel(const T* __restrict__ rows, int row_stride, const int* __restr
 // ------------------------------------------------------------------------------------------ tensor cores
 constexpr int DC = 64, DVB = 32, DC_THREADS = 128;     // tokens per chunk, value columns per CTA
 
+// q, k, v of a row in place: act(x) as the rows' type holds it (the chunked kernel then copies tiles as they are)
+template <typename T>
+__global__ void silu_rows_kernel(T* __restrict__ rows, int row_stride, int width, long long count) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
+    T* at = rows + (i / width) * row_stride + (i % width);
+    *at = from_float<T>(silu_f(to_float(*at)));
+  }
+}
+
 template <int DIM>
 __global__ void __launch_bounds__(DC_THREADS)
 decay_chunks_kernel(const __nv_bfloat16* __restrict__ rows, int row_stride, const int* __restrict__ q_start,
                     const int* __restrict__ state_slots, float* __restrict__ state, int num_slots,
-                    const float* __restrict__ decay, float* __restrict__ out, int heads, int vdim, int act, int* status) {
+                    const float* __restrict__ decay, float* __restrict__ out, int heads, int vdim, int* status) {
   constexpr int QS = DIM + 8, VS = DVB + 8, MT = DIM / 64;        // a warp owns DIM / 4 rows of the state: MT tiles of 16
+  constexpr int QCH = DIM / 8, VCH = DVB / 8;
   extern __shared__ __align__(16) unsigned char dc_smem[];
-  __nv_bfloat16* sQ = (__nv_bfloat16*)dc_smem;                    // DC x QS
-  __nv_bfloat16* sK = sQ + DC * QS;
-  __nv_bfloat16* sKh = sK + DC * QS;                              // decayed keys, high and low terms
+  __nv_bfloat16* sQ = (__nv_bfloat16*)dc_smem;                    // 2 x DC x QS
+  __nv_bfloat16* sK = sQ + 2 * DC * QS;                           // 2 x DC x QS
+  __nv_bfloat16* sKh = sK + 2 * DC * QS;                          // decayed keys, high and low terms
   __nv_bfloat16* sKl = sKh + DC * QS;
-  __nv_bfloat16* sV = sKl + DC * QS;                              // DC x VS
-  __nv_bfloat16* sSh = sV + DC * VS;                              // DIM x VS: the state, high and low terms
+  __nv_bfloat16* sV = sKl + DC * QS;                              // 2 x DC x VS
+  __nv_bfloat16* sSh = sV + 2 * DC * VS;                          // DIM x VS: the state, high and low terms
   __nv_bfloat16* sSl = sSh + DIM * VS;
+  __shared__ float power[DC + 1];                                 // decay^e
   pdl_launch_dependents();
-  pdl_wait();
   const int r = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * DVB;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gr = lane >> 2, qc = lane & 3;
+  if (tid <= DC) power[tid] = exp2f((float)tid * log2f(decay[h]));
+  pdl_wait();
   const int slot = state_slots[r];
   if (slot < 0 || slot >= num_slots) {
     if (tid == 0) atomicOr(status, SPROUT_STATUS_BAD_PAGE);
     return;
   }
   float* mine = state + (((size_t)slot * heads + h) * DIM) * vdim;
-  const float lam = decay[h], log_lam = log2f(lam);
   float S[MT][DVB / 8][4];
 #pragma unroll
   for (int mt = 0; mt < MT; mt++)
@@ -115,30 +128,57 @@ decay_chunks_kernel(const __nv_bfloat16* __restrict__ rows, int row_stride, cons
         S[mt][nt][c] = col < vdim ? mine[(size_t)row * vdim + col] : 0.f;
       }
   const int first = q_start[r], last = q_start[r + 1];
-  for (int t0 = first; t0 < last; t0 += DC) {
+  auto load = [&](int buf, int t0) {
     const int n = min(DC, last - t0);
-    __syncthreads();                                   // the chunk before is done with shared memory
-    // q, k (activated, as bfloat16 holds them), the decayed keys in two terms, v
-    for (int idx = tid; idx < DC * DIM; idx += DC_THREADS) {
-      const int j = idx / DIM, d = idx % DIM;
-      float q = 0.f, k = 0.f;
+    for (int idx = tid; idx < DC * QCH; idx += DC_THREADS) {
+      const int j = idx / QCH, c = (idx % QCH) * 8;
+      __nv_bfloat16* dq = sQ + (buf * DC + j) * QS + c;
+      __nv_bfloat16* dk = sK + (buf * DC + j) * QS + c;
       if (j < n) {
-        const __nv_bfloat16* row = rows + (size_t)(t0 + j) * row_stride + (size_t)h * DIM + d;
-        q = activate(row[0], act);
-        k = activate(row[(size_t)heads * DIM], act);
+        const __nv_bfloat16* src = rows + (size_t)(t0 + j) * row_stride + (size_t)h * DIM + c;
+        cp_async16(dq, src);
+        cp_async16(dk, src + (size_t)heads * DIM);
+      } else {
+        *(uint4*)dq = make_uint4(0, 0, 0, 0);
+        *(uint4*)dk = make_uint4(0, 0, 0, 0);
       }
-      sQ[j * QS + d] = __float2bfloat16_rn(q);
-      sK[j * QS + d] = __float2bfloat16_rn(k);
-      const float kd = k * exp2f((float)(n - 1 - j) * log_lam);
-      const __nv_bfloat16 hi = __float2bfloat16_rn(kd);
-      sKh[j * QS + d] = hi;
-      sKl[j * QS + d] = __float2bfloat16_rn(kd - __bfloat162float(hi));
     }
-    for (int idx = tid; idx < DC * DVB; idx += DC_THREADS) {
-      const int j = idx / DVB, c = idx % DVB;
-      float v = 0.f;
-      if (j < n && col0 + c < vdim) v = activate(rows[(size_t)(t0 + j) * row_stride + (size_t)2 * heads * DIM + (size_t)h * vdim + col0 + c], act);
-      sV[j * VS + c] = __float2bfloat16_rn(v);
+    for (int idx = tid; idx < DC * VCH; idx += DC_THREADS) {
+      const int j = idx / VCH, c = (idx % VCH) * 8;
+      __nv_bfloat16* dv = sV + (buf * DC + j) * VS + c;
+      if (j < n && col0 + c < vdim) cp_async16(dv, rows + (size_t)(t0 + j) * row_stride + (size_t)2 * heads * DIM + (size_t)h * vdim + col0 + c);
+      else *(uint4*)dv = make_uint4(0, 0, 0, 0);
+    }
+  };
+  if (first < last) load(0, first);
+  cp_async_commit();
+  int buf = 0;
+  for (int t0 = first; t0 < last; t0 += DC, buf ^= 1) {
+    const int n = min(DC, last - t0);
+    cp_async_wait<0>();
+    __syncthreads();                                   // the chunk has landed; the chunk before is done with shared memory
+    if (t0 + DC < last) load(buf ^ 1, t0 + DC);
+    cp_async_commit();
+    const __nv_bfloat16* tQ = sQ + buf * DC * QS;
+    const __nv_bfloat16* tK = sK + buf * DC * QS;
+    const __nv_bfloat16* tV = sV + buf * DC * VS;
+    // the decayed keys in two terms
+    for (int idx = tid; idx < DC * QCH; idx += DC_THREADS) {
+      const int j = idx / QCH, c = (idx % QCH) * 8;
+      const float w = j < n ? power[n - 1 - j] : 0.f;
+      const uint4 raw = *(const uint4*)(tK + j * QS + c);
+      const __nv_bfloat162* pair = (const __nv_bfloat162*)&raw;
+      uint4 hi, lo;
+      __nv_bfloat162* ph = (__nv_bfloat162*)&hi;
+      __nv_bfloat162* pl = (__nv_bfloat162*)&lo;
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const float a = __low2float(pair[e]) * w, b = __high2float(pair[e]) * w;
+        ph[e] = __floats2bfloat162_rn(a, b);
+        pl[e] = __floats2bfloat162_rn(a - __low2float(ph[e]), b - __high2float(ph[e]));
+      }
+      *(uint4*)(sKh + j * QS + c) = hi;
+      *(uint4*)(sKl + j * QS + c) = lo;
     }
 #pragma unroll
     for (int mt = 0; mt < MT; mt++)
@@ -164,11 +204,11 @@ decay_chunks_kernel(const __nv_bfloat16* __restrict__ rows, int row_stride, cons
 #pragma unroll
     for (int kk = 0; kk < DIM / 16; kk++) {
       uint32_t a[4];
-      ldmatrix_x4(a, sQ + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * QS + kk * 16 + (lane >> 4) * 8);
+      ldmatrix_x4(a, tQ + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * QS + kk * 16 + (lane >> 4) * 8);
 #pragma unroll
       for (int n2 = 0; n2 < DC / 16; n2++) {
         uint32_t b[4];
-        ldmatrix_x4(b, sK + (n2 * 16 + (lane & 7) + (lane >> 4) * 8) * QS + kk * 16 + ((lane >> 3) & 1) * 8);
+        ldmatrix_x4(b, tK + (n2 * 16 + (lane & 7) + (lane >> 4) * 8) * QS + kk * 16 + ((lane >> 3) & 1) * 8);
         mma_bf16(s[2 * n2], a, b[0], b[1]);
         mma_bf16(s[2 * n2 + 1], a, b[2], b[3]);
       }
@@ -185,7 +225,7 @@ decay_chunks_kernel(const __nv_bfloat16* __restrict__ rows, int row_stride, cons
       }
     }
     const int i0 = warp * 16 + gr, i1 = i0 + 8;        // the thread's two rows (tokens of the chunk)
-    const float carry0 = exp2f((float)(i0 + 1) * log_lam), carry1 = exp2f((float)(i1 + 1) * log_lam);
+    const float carry0 = power[i0 + 1], carry1 = power[i1 + 1];
 #pragma unroll
     for (int i = 0; i < DVB / 8; i++) { o[i][0] *= carry0; o[i][1] *= carry0; o[i][2] *= carry1; o[i][3] *= carry1; }
 #pragma unroll
@@ -193,8 +233,8 @@ decay_chunks_kernel(const __nv_bfloat16* __restrict__ rows, int row_stride, cons
 #pragma unroll
       for (int c = 0; c < 2; c++) {
         const int j = i * 8 + qc * 2 + c;
-        s[i][c] = j <= i0 ? s[i][c] * exp2f((float)(i0 - j) * log_lam) : 0.f;
-        s[i][2 + c] = j <= i1 ? s[i][2 + c] * exp2f((float)(i1 - j) * log_lam) : 0.f;
+        s[i][c] = j <= i0 ? s[i][c] * power[i0 - j] : 0.f;
+        s[i][2 + c] = j <= i1 ? s[i][2 + c] * power[i1 - j] : 0.f;
       }
     }
 #pragma unroll
@@ -207,7 +247,7 @@ decay_chunks_kernel(const __nv_bfloat16* __restrict__ rows, int row_stride, cons
 #pragma unroll
       for (int d2 = 0; d2 < DVB / 16; d2++) {
         uint32_t b[4];
-        ldmatrix_x4_trans(b, sV + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS + d2 * 16 + (lane >> 4) * 8);
+        ldmatrix_x4_trans(b, tV + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS + d2 * 16 + (lane >> 4) * 8);
         mma_bf16(o[2 * d2], a, b[0], b[1]);
         mma_bf16(o[2 * d2 + 1], a, b[2], b[3]);
       }
@@ -220,13 +260,12 @@ decay_chunks_kernel(const __nv_bfloat16* __restrict__ rows, int row_stride, cons
 #pragma unroll
       for (int nt = 0; nt < DVB / 8; nt++) {
         const int col = nt * 8 + qc * 2;
-        if (col0 + col < vdim) dst[col] = o[nt][half * 2];
-        if (col0 + col + 1 < vdim) dst[col + 1] = o[nt][half * 2 + 1];
+        if (col0 + col < vdim) *(float2*)(dst + col) = make_float2(o[nt][half * 2], o[nt][half * 2 + 1]);
       }
     }
 
     // the state after the chunk: decay^n S + (decayed keys)^T V, the keys' two terms one after the other
-    const float shrink = exp2f((float)n * log_lam);
+    const float shrink = power[n];
 #pragma unroll
     for (int mt = 0; mt < MT; mt++) {
 #pragma unroll
@@ -243,7 +282,7 @@ decay_chunks_kernel(const __nv_bfloat16* __restrict__ rows, int row_stride, cons
 #pragma unroll
         for (int d2 = 0; d2 < DVB / 16; d2++) {
           uint32_t b[4];
-          ldmatrix_x4_trans(b, sV + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS + d2 * 16 + (lane >> 4) * 8);
+          ldmatrix_x4_trans(b, tV + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VS + d2 * 16 + (lane >> 4) * 8);
           mma_bf16(S[mt][2 * d2], ah, b[0], b[1]);
           mma_bf16(S[mt][2 * d2 + 1], ah, b[2], b[3]);
           mma_bf16(S[mt][2 * d2], al, b[0], b[1]);
@@ -252,6 +291,7 @@ decay_chunks_kernel(const __nv_bfloat16* __restrict__ rows, int row_stride, cons
       }
     }
   }
+  cp_async_wait<0>();
 #pragma unroll
   for (int mt = 0; mt < MT; mt++)
 #pragma unroll
@@ -265,34 +305,45 @@ decay_chunks_kernel(const __nv_bfloat16* __restrict__ rows, int row_stride, cons
 
 template <int DIM>
 int launch_chunks(const void* rows, int row_stride, const int* q_start, const int* state_slots, float* state, int num_slots,
-                  const float* decay, float* out, int requests, int heads, int vdim, int act, int* status, cudaStream_t stream) {
-  const int smem = (4 * DC * (DIM + 8) + DC * (DVB + 8) + 2 * DIM * (DVB + 8)) * 2;
+                  const float* decay, float* out, int requests, int heads, int vdim, int* status, cudaStream_t stream) {
+  const int smem = (6 * DC * (DIM + 8) + 2 * DC * (DVB + 8) + 2 * DIM * (DVB + 8)) * 2;
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(decay_chunks_kernel<DIM>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     configured = true;
   }
   sprout_launch(decay_chunks_kernel<DIM>, dim3(requests, heads, (vdim + DVB - 1) / DVB), dim3(DC_THREADS), smem, stream,
-                (const __nv_bfloat16*)rows, row_stride, q_start, state_slots, state, num_slots, decay, out, heads, vdim, act, status);
+                (const __nv_bfloat16*)rows, row_stride, q_start, state_slots, state, num_slots, decay, out, heads, vdim, status);
   return sprout_check_launch("decay_chunks");
 }
 
 }  // namespace
 
-SPROUT_API int sprout_decay_chunks_supported(int dim) { return dim == 64 || dim == 128; }
+// The chunked kernel copies 16-byte pieces of the rows: key vectors of 64 or 128, value rows and row strides in multiples of 8.
+SPROUT_API int sprout_decay_chunks_supported(int dim, int vdim, int row_stride) {
+  return (dim == 64 || dim == 128) && vdim % 8 == 0 && row_stride % 8 == 0;
+}
 
-// The same as decay_scan for bfloat16 rows, 64 tokens at a time on tensor cores.
-SPROUT_API int sprout_decay_chunks(const void* rows, int row_stride, const int* q_start, const int* state_slots, float* state,
-                                   int num_slots, const float* decay, float* out, int requests, int heads, int dim, int vdim,
-                                   int act, int* status, cudaStream_t stream) {
+// The same as decay_scan for bfloat16 rows, 64 tokens at a time on tensor cores.  With `act` the first
+// heads * (2 dim + vdim) elements of every row are replaced by their activation first (in place).
+SPROUT_API int sprout_decay_chunks(void* rows, int row_stride, const int* q_start, const int* state_slots, float* state,
+                                   int num_slots, const float* decay, float* out, int tokens, int requests, int heads, int dim,
+                                   int vdim, int act, int* status, cudaStream_t stream) {
   SPROUT_REQUIRE(rows && q_start && state_slots && state && decay && out && status, "decay_chunks: null pointer");
-  SPROUT_REQUIRE(requests > 0 && heads > 0 && vdim > 0 && num_slots > 0 && heads <= 65535, "decay_chunks: bad sizes");
+  SPROUT_REQUIRE(tokens > 0 && requests > 0 && heads > 0 && vdim > 0 && num_slots > 0 && heads <= 65535, "decay_chunks: bad sizes");
   SPROUT_REQUIRE(row_stride >= heads * (2 * dim + vdim), "decay_chunks: rows too short");
+  SPROUT_REQUIRE(sprout_decay_chunks_supported(dim, vdim, row_stride) && ((uintptr_t)rows & 15) == 0 && ((uintptr_t)out & 7) == 0,
+                 "decay_chunks: key vectors of 64 or 128 elements, rows in 16-byte pieces (dim %d, vdim %d, stride %d)", dim, vdim, row_stride);
+  if (act) {
+    const int width = heads * (2 * dim + vdim);
+    const long long count = (long long)tokens * width;
+    const int grid = (int)((count + 255) / 256 < 148 * 16 ? (count + 255) / 256 : 148 * 16);
+    sprout_launch(silu_rows_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, (__nv_bfloat16*)rows, row_stride, width, count);
+    if (int code = sprout_check_launch("silu_rows")) return code;
+  }
   if (dim == 64)
-    return launch_chunks<64>(rows, row_stride, q_start, state_slots, state, num_slots, decay, out, requests, heads, vdim, act, status, stream);
-  if (dim == 128)
-    return launch_chunks<128>(rows, row_stride, q_start, state_slots, state, num_slots, decay, out, requests, heads, vdim, act, status, stream);
-  return sprout_fail("decay_chunks: key vectors of 64 or 128 elements (got %d)", dim);
+    return launch_chunks<64>(rows, row_stride, q_start, state_slots, state, num_slots, decay, out, requests, heads, vdim, status, stream);
+  return launch_chunks<128>(rows, row_stride, q_start, state_slots, state, num_slots, decay, out, requests, heads, vdim, status, stream);
 }
 
 // rows [tokens, row_stride] (dtype), out float32 [tokens, heads * vdim], state float32 [slots, heads, dim, vdim].

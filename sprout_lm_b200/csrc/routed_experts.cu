@@ -23,30 +23,42 @@ using namespace sprout_attn;
 
 namespace {
 
-constexpr int ROUTE_WARPS = 4;
+constexpr int ROUTE_THREADS = 256;
 
+// One block per token: the warps share the router's outputs (warp w takes outputs w, w + 8, ...), a lane sums every
+// 32nd element in four independent chains, the lanes are added in a fixed order; warp 0 then takes the softmax and the
+// choices.  Nothing depends on the other tokens of the batch.
 template <typename T>
-__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+__global__ void __launch_bounds__(ROUTE_THREADS)
 moe_route_kernel(const T* __restrict__ h, int h_stride, const float* __restrict__ router, const float* __restrict__ correction,
                  int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ counts, int tokens, int width,
                  int outputs, int experts, int top, float scale) {
   extern __shared__ float smem[];
+  float* z = smem;                    // outputs: scores
+  float* choice = z + outputs;        // outputs
+  float* row = choice + outputs;      // width: the token's h as float32
   pdl_launch_dependents();
   pdl_wait();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * ROUTE_WARPS + warp;
-  if (t >= tokens) return;
-  float* z = smem + (size_t)warp * 2 * outputs;     // scores, then choices
-  float* choice = z + outputs;
-  const T* row = h + (size_t)t * h_stride;
-  for (int e = 0; e < outputs; e++) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = blockIdx.x;
+  const T* src = h + (size_t)t * h_stride;
+  for (int k = threadIdx.x; k < width; k += ROUTE_THREADS) row[k] = to_float(src[k]);
+  __syncthreads();
+  for (int e = warp; e < outputs; e += ROUTE_THREADS / 32) {
     const float* w = router + (size_t)e * width;
-    float dot = 0.f;
-    for (int k = lane; k < width; k += 32) dot = fmaf(to_float(row[k]), w[k], dot);
-    dot = warp_sum(dot);
+    float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+    int k = lane;
+    for (; k + 96 < width; k += 128) {
+      d0 = fmaf(row[k], w[k], d0);
+      d1 = fmaf(row[k + 32], w[k + 32], d1);
+      d2 = fmaf(row[k + 64], w[k + 64], d2);
+      d3 = fmaf(row[k + 96], w[k + 96], d3);
+    }
+    for (; k < width; k += 32) d0 = fmaf(row[k], w[k], d0);
+    const float dot = warp_sum((d0 + d1) + (d2 + d3));
     if (lane == 0) z[e] = dot;
   }
-  __syncwarp();
+  __syncthreads();
+  if (warp != 0) return;
   float top_z = -INFINITY;
   for (int e = lane; e < outputs; e += 32) top_z = fmaxf(top_z, z[e]);
   top_z = warp_max(top_z);
@@ -60,26 +72,38 @@ moe_route_kernel(const T* __restrict__ h, int h_stride, const float* __restrict_
     choice[e] = s + correction[e];
   }
   __syncwarp();
-  if (lane == 0) {
-    float taken = 0.f;
-    for (int place = 0; place < top; place++) {
-      int best = -1;
-      float best_c = -INFINITY;
-      for (int e = 0; e < outputs; e++)
-        if (choice[e] > best_c) {
-          best_c = choice[e];
-          best = e;
-        }
-      if (best < 0) best = 0;          // non-finite scores: the status of the logits will tell
+  // the largest choice `top` times; among equals the lowest index
+  float taken = 0.f;
+  for (int place = 0; place < top; place++) {
+    float best_c = -INFINITY;
+    int best = 0x7fffffff;
+    for (int e = lane; e < outputs; e += 32)
+      if (choice[e] > best_c) {
+        best_c = choice[e];
+        best = e;
+      }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float other_c = __shfl_xor_sync(0xffffffffu, best_c, o);
+      const int other = __shfl_xor_sync(0xffffffffu, best, o);
+      if (other_c > best_c || (other_c == best_c && other < best)) {
+        best_c = other_c;
+        best = other;
+      }
+    }
+    if (best >= outputs) best = 0;     // non-finite scores: the status of the logits will tell
+    taken += z[best];
+    if (lane == 0) {
       choice[best] = -INFINITY;
       ids[(size_t)t * top + place] = best;
       weights[(size_t)t * top + place] = z[best];
-      taken += z[best];
       if (best < experts) atomicAdd(&counts[best], 1);
     }
-    const float norm = scale / (taken + 1e-20f);
-    for (int place = 0; place < top; place++) weights[(size_t)t * top + place] *= norm;
+    __syncwarp();
   }
+  const float norm = scale / (taken + 1e-20f);
+  __syncwarp();
+  for (int place = lane; place < top; place += 32) weights[(size_t)t * top + place] *= norm;
 }
 
 // One block.  counts -> offsets [experts + 1]; counts are left zeroed for the next call.
@@ -352,14 +376,14 @@ SPROUT_API int sprout_moe_route(const void* h, int h_stride, int dtype, const fl
   SPROUT_REQUIRE(h && router && correction && ids && weights && counts, "moe_route: null pointer");
   SPROUT_REQUIRE(tokens > 0 && width > 0 && outputs > 0 && experts >= 0 && experts <= outputs && top > 0 && top <= outputs,
                  "moe_route: bad sizes (outputs %d, experts %d, top %d)", outputs, experts, top);
-  const size_t smem = (size_t)ROUTE_WARPS * 2 * outputs * sizeof(float);
-  SPROUT_REQUIRE(smem <= 48 * 1024, "moe_route: too many router outputs (%d)", outputs);
-  dim3 grid((tokens + ROUTE_WARPS - 1) / ROUTE_WARPS);
+  const size_t smem = (size_t)(2 * outputs + width) * sizeof(float);
+  SPROUT_REQUIRE(smem <= 48 * 1024, "moe_route: too many router outputs (%d) or too wide rows (%d)", outputs, width);
+  dim3 grid(tokens);
   if (dtype == SPROUT_F32)
-    sprout_launch(moe_route_kernel<float>, grid, dim3(ROUTE_WARPS * 32), smem, stream, (const float*)h, h_stride, router,
+    sprout_launch(moe_route_kernel<float>, grid, dim3(ROUTE_THREADS), smem, stream, (const float*)h, h_stride, router,
                   correction, ids, weights, counts, tokens, width, outputs, experts, top, scale);
   else if (dtype == SPROUT_BF16)
-    sprout_launch(moe_route_kernel<__nv_bfloat16>, grid, dim3(ROUTE_WARPS * 32), smem, stream, (const __nv_bfloat16*)h, h_stride,
+    sprout_launch(moe_route_kernel<__nv_bfloat16>, grid, dim3(ROUTE_THREADS), smem, stream, (const __nv_bfloat16*)h, h_stride,
                   router, correction, ids, weights, counts, tokens, width, outputs, experts, top, scale);
   else
     return sprout_fail("moe_route: unknown dtype %d", dtype);

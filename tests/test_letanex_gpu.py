@@ -198,7 +198,7 @@ def test_decay_scan_carries_state(dtype, sizes):
     rng = np.random.default_rng(heads + dim)
     lengths = [70, 1, 33, 150]
     width = heads * (2 * dim + vdim)
-    raw = [rounded(rng.normal(0, 1.0, size=(n, width + 5)), dtype) for n in lengths]      # rows wider than q | k | v
+    raw = [rounded(rng.normal(0, 1.0, size=(n, width + 8)), dtype) for n in lengths]      # rows wider than q | k | v
     state = torch.full((3, heads, dim, vdim), float("nan"), device=DEV)
     decay_t = dev(np.asarray(decay, dtype=np.float32))
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
