@@ -199,7 +199,7 @@ struct MultiMapParams {
   int* status;
 };
 
-template <int DIM, int VDIM, int MAPS>
+template <int DIM, int VDIM, int MAPS, bool SPLIT>
 __global__ void __launch_bounds__(MM_THREADS)
 multimap_attention_mma_kernel(const MultiMapParams p) {
   constexpr int KW = MAPS * DIM, KSTRIDE = KW + 8, VSTRIDE = VDIM + 8, KCHUNKS = KW / 8, VCHUNKS = VDIM / 8;
@@ -281,8 +281,14 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
   load_tile(0);
   cp_async_commit();
 
+  // SPLIT (a step in which no request has more than 16 rows: single tokens, the heads of one key/value group): a CTA
+  // divides every tile's keys among its warps instead of its rows, and the warps' partial results are merged at the end.
+  constexpr bool split = SPLIT;
+  const int qrow = split ? 0 : warp * 16;             // the warp's 16 rows
+  constexpr int nk = split ? 1 : MM_KEYS / 16;        // blocks of 16 keys of a tile that the warp takes, from key kb on
+  const int kb = split ? warp * 16 : 0;
   const int gr = lane >> 2, qc = lane & 3;
-  const int my_row0 = warp * 16 + gr, my_row1 = my_row0 + 8;
+  const int my_row0 = qrow + gr, my_row1 = my_row0 + 8;
   const int limit0 = s_limit[my_row0], limit1 = s_limit[my_row1];
   float m0[MAPS], m1[MAPS], l0[MAPS], l1[MAPS];
   float o[MAPS][VDIM / 8][4];
@@ -294,7 +300,7 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
     for (int i = 0; i < VDIM / 8; i++) o[m][i][0] = o[m][i][1] = o[m][i][2] = o[m][i][3] = 0.f;
   }
   const float scale_log2 = p.scale * 1.4426950408889634f;
-  const int warp_min_limit = s_limit[min(warp * 16, last_row)];
+  const int warp_min_limit = s_limit[min(qrow, last_row)];
 
   for (int t = 0; t < kv_tiles; t++) {
     const int buf = t & 1;
@@ -307,7 +313,7 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
     const __nv_bfloat16* tK = sK + buf * MM_KEYS * KSTRIDE;
     const __nv_bfloat16* tV = sV + buf * MM_KEYS * VSTRIDE;
     const int kv0 = t * MM_KEYS;
-    if (kv0 > s_limit[min(warp * 16 + 15, last_row)]) continue;       // no row of this warp sees the tile
+    if (kv0 + kb > s_limit[min(qrow + 15, last_row)]) continue;       // no row of this warp sees its keys of the tile
 #pragma unroll
     for (int m = 0; m < MAPS; m++) {
       float s[MM_KEYS / 8][4];
@@ -316,20 +322,22 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
 #pragma unroll
       for (int kk = 0; kk < DIM / 16; kk++) {
         uint32_t a[4];
-        ldmatrix_x4(a, sQ + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KSTRIDE + m * DIM + kk * 16 + (lane >> 4) * 8);
+        ldmatrix_x4(a, sQ + (qrow + (lane & 7) + ((lane >> 3) & 1) * 8) * KSTRIDE + m * DIM + kk * 16 + (lane >> 4) * 8);
 #pragma unroll
         for (int n2 = 0; n2 < MM_KEYS / 16; n2++) {
+          if (n2 >= nk) break;
           uint32_t b[4];
-          ldmatrix_x4(b, tK + (n2 * 16 + (lane & 7) + (lane >> 4) * 8) * KSTRIDE + m * DIM + kk * 16 + ((lane >> 3) & 1) * 8);
+          ldmatrix_x4(b, tK + (kb + n2 * 16 + (lane & 7) + (lane >> 4) * 8) * KSTRIDE + m * DIM + kk * 16 + ((lane >> 3) & 1) * 8);
           mma_bf16(s[2 * n2], a, b[0], b[1]);
           mma_bf16(s[2 * n2 + 1], a, b[2], b[3]);
         }
       }
       float t_max0 = -INFINITY, t_max1 = -INFINITY;
-      if (kv0 + MM_KEYS - 1 > warp_min_limit) {
+      if (kv0 + kb + nk * 16 - 1 > warp_min_limit) {
 #pragma unroll
         for (int i = 0; i < MM_KEYS / 8; i++) {
-          const int key = kv0 + i * 8 + qc * 2;
+          if (i >= 2 * nk) break;
+          const int key = kv0 + kb + i * 8 + qc * 2;
           if (key > limit0) s[i][0] = -INFINITY;
           if (key + 1 > limit0) s[i][1] = -INFINITY;
           if (key > limit1) s[i][2] = -INFINITY;
@@ -338,6 +346,7 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
       }
 #pragma unroll
       for (int i = 0; i < MM_KEYS / 8; i++) {
+        if (i >= 2 * nk) break;
         t_max0 = fmaxf(t_max0, fmaxf(s[i][0], s[i][1]));
         t_max1 = fmaxf(t_max1, fmaxf(s[i][2], s[i][3]));
       }
@@ -355,6 +364,7 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
       for (int i = 0; i < VDIM / 8; i++) { o[m][i][0] *= alpha0; o[m][i][1] *= alpha0; o[m][i][2] *= alpha1; o[m][i][3] *= alpha1; }
 #pragma unroll
       for (int i = 0; i < MM_KEYS / 8; i++) {
+        if (i >= 2 * nk) break;
         s[i][0] = exp2f(fmaf(s[i][0], scale_log2, -base0)); s[i][1] = exp2f(fmaf(s[i][1], scale_log2, -base0));
         s[i][2] = exp2f(fmaf(s[i][2], scale_log2, -base1)); s[i][3] = exp2f(fmaf(s[i][3], scale_log2, -base1));
         l0[m] += s[i][0] + s[i][1];
@@ -362,6 +372,7 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
       }
 #pragma unroll
       for (int kk = 0; kk < MM_KEYS / 16; kk++) {
+        if (kk >= nk) break;
         uint32_t a[4];
         a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
         a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
@@ -370,7 +381,7 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
 #pragma unroll
         for (int d2 = 0; d2 < VDIM / 16; d2++) {
           uint32_t b[4];
-          ldmatrix_x4_trans(b, tV + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VSTRIDE + d2 * 16 + (lane >> 4) * 8);
+          ldmatrix_x4_trans(b, tV + (kb + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VSTRIDE + d2 * 16 + (lane >> 4) * 8);
           mma_bf16(o[m][2 * d2], a, b[0], b[1]);
           mma_bf16(o[m][2 * d2 + 1], a, b[2], b[3]);
         }
@@ -385,6 +396,53 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
   for (int m = 0; m < MAPS; m++) {
     l0[m] += __shfl_xor_sync(0xffffffffu, l0[m], 1); l0[m] += __shfl_xor_sync(0xffffffffu, l0[m], 2);
     l1[m] += __shfl_xor_sync(0xffffffffu, l1[m], 1); l1[m] += __shfl_xor_sync(0xffffffffu, l1[m], 2);
+  }
+  if (split) {
+    // the warps hold the same rows over different keys: warp 0 merges them, in the warps' order
+    constexpr int PER = MAPS * (VDIM / 8 * 4 + 4);
+    float* slots = (float*)mm_smem;
+    __syncthreads();                                   // the tiles are no longer read
+    float* mine = slots + (size_t)(warp * 32 + lane) * PER;
+#pragma unroll
+    for (int m = 0; m < MAPS; m++) {
+      float* at = mine + m * (VDIM / 8 * 4 + 4);
+      at[0] = m0[m]; at[1] = m1[m]; at[2] = l0[m]; at[3] = l1[m];
+#pragma unroll
+      for (int i = 0; i < VDIM / 8; i++)
+#pragma unroll
+        for (int c = 0; c < 4; c++) at[4 + i * 4 + c] = o[m][i][c];
+    }
+    __syncthreads();
+    if (warp != 0) return;
+#pragma unroll
+    for (int m = 0; m < MAPS; m++) {
+      float top0 = -INFINITY, top1 = -INFINITY;
+      for (int w = 0; w < MM_THREADS / 32; w++) {
+        const float* at = slots + (size_t)(w * 32 + lane) * PER + m * (VDIM / 8 * 4 + 4);
+        top0 = fmaxf(top0, at[0]);
+        top1 = fmaxf(top1, at[1]);
+      }
+      l0[m] = l1[m] = 0.f;
+#pragma unroll
+      for (int i = 0; i < VDIM / 8; i++) o[m][i][0] = o[m][i][1] = o[m][i][2] = o[m][i][3] = 0.f;
+      for (int w = 0; w < MM_THREADS / 32; w++) {
+        const float* at = slots + (size_t)(w * 32 + lane) * PER + m * (VDIM / 8 * 4 + 4);
+        const float f0 = at[0] == -INFINITY ? 0.f : exp2f((at[0] - top0) * scale_log2);
+        const float f1 = at[1] == -INFINITY ? 0.f : exp2f((at[1] - top1) * scale_log2);
+        l0[m] = fmaf(at[2], f0, l0[m]);
+        l1[m] = fmaf(at[3], f1, l1[m]);
+#pragma unroll
+        for (int i = 0; i < VDIM / 8; i++) {
+          o[m][i][0] = fmaf(at[4 + i * 4], f0, o[m][i][0]);
+          o[m][i][1] = fmaf(at[4 + i * 4 + 1], f0, o[m][i][1]);
+          o[m][i][2] = fmaf(at[4 + i * 4 + 2], f1, o[m][i][2]);
+          o[m][i][3] = fmaf(at[4 + i * 4 + 3], f1, o[m][i][3]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < MAPS; m++) {
     inv0[m] = 1.0f / l0[m];
     inv1[m] = 1.0f / l1[m];
   }
@@ -423,16 +481,18 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
   }
 }
 
-template <int DIM, int VDIM, int MAPS>
+template <int DIM, int VDIM, int MAPS, bool SPLIT>
 int launch_multimap(const MultiMapParams& p, int grid_x, cudaStream_t stream) {
-  const int smem = (3 * MM_ROWS * (MAPS * DIM + 8) + 2 * MM_KEYS * (VDIM + 8)) * 2;
+  const int tiles_bytes = (3 * MM_ROWS * (MAPS * DIM + 8) + 2 * MM_KEYS * (VDIM + 8)) * 2;
+  const int merge_bytes = MM_THREADS * MAPS * (VDIM / 8 * 4 + 4) * 4;         // the warps' partial results of a 16-row CTA
+  const int smem = tiles_bytes > merge_bytes ? tiles_bytes : merge_bytes;
   static bool configured = false;
   if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(multimap_attention_mma_kernel<DIM, VDIM, MAPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t err = cudaFuncSetAttribute(multimap_attention_mma_kernel<DIM, VDIM, MAPS, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (err != cudaSuccess) return sprout_fail("multimap_attention_mma: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(err));
     configured = true;
   }
-  sprout_launch(multimap_attention_mma_kernel<DIM, VDIM, MAPS>, dim3(grid_x, p.kv_heads), dim3(MM_THREADS), smem, stream, p);
+  sprout_launch(multimap_attention_mma_kernel<DIM, VDIM, MAPS, SPLIT>, dim3(grid_x, p.kv_heads), dim3(MM_THREADS), smem, stream, p);
   return sprout_check_launch("multimap_attention_mma");
 }
 
@@ -446,16 +506,16 @@ bool mma_sizes(int maps, int dim, int vdim) {
 SPROUT_API int sprout_multimap_attention_mma_supported(int maps, int dim, int vdim) { return mma_sizes(maps, dim, vdim) ? 1 : 0; }
 
 // bfloat16 only.  `tiles` bounds the (request, 64 rows) tiles of the batch: sum over requests of
-// ceil(tokens * heads / kv_heads / 64), or any larger number.
+// ceil(tokens * heads / kv_heads / 64), or any larger number; `max_q_len` is the most tokens any request brings.
 SPROUT_API int sprout_multimap_attention_mma(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                              const int* block_table, int table_stride, const int* q_start,
                                              const int* positions, void* out, int out_stride, int requests, int tiles,
-                                             int heads, int kv_heads, int maps, int dim, int vdim, int page_tokens,
+                                             int max_q_len, int heads, int kv_heads, int maps, int dim, int vdim, int page_tokens,
                                              int num_pages, float scale, float lambda, float norm_eps, float out_scale,
                                              int* status, cudaStream_t stream) {
   SPROUT_REQUIRE(q && k_cache && v_cache && block_table && q_start && positions && out && status, "multimap_attention_mma: null pointer");
-  SPROUT_REQUIRE(requests > 0 && tiles > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && page_tokens > 0 && num_pages > 0,
-                 "multimap_attention_mma: bad sizes");
+  SPROUT_REQUIRE(requests > 0 && tiles > 0 && max_q_len > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && page_tokens > 0 &&
+                 num_pages > 0, "multimap_attention_mma: bad sizes");
   SPROUT_REQUIRE(mma_sizes(maps, dim, vdim), "multimap_attention_mma: no kernel for %d maps of %d with values of %d", maps, dim, vdim);
   SPROUT_REQUIRE(q_stride % 8 == 0 && out_stride % 2 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)k_cache & 15) == 0 &&
                  ((uintptr_t)v_cache & 15) == 0 && ((uintptr_t)out & 3) == 0, "multimap_attention_mma: rows must start on 16-byte boundaries");
@@ -463,9 +523,12 @@ SPROUT_API int sprout_multimap_attention_mma(const void* q, int q_stride, const 
   MultiMapParams p{(const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
                    table_stride, q_start, positions, (__nv_bfloat16*)out, out_stride, requests, heads, kv_heads, page_tokens,
                    num_pages, scale, lambda, norm_eps, out_scale, status};
-#define PICK(D, V)                                                                              \
-  if (dim == D && vdim == V)                                                                    \
-    return maps == 2 ? launch_multimap<D, V, 2>(p, tiles, stream) : launch_multimap<D, V, 1>(p, tiles, stream);
+  const bool split = max_q_len * (heads / kv_heads) <= 16;
+#define PICK(D, V)                                                                                              \
+  if (dim == D && vdim == V) {                                                                                  \
+    if (split) return maps == 2 ? launch_multimap<D, V, 2, true>(p, tiles, stream) : launch_multimap<D, V, 1, true>(p, tiles, stream); \
+    return maps == 2 ? launch_multimap<D, V, 2, false>(p, tiles, stream) : launch_multimap<D, V, 1, false>(p, tiles, stream);         \
+  }
   PICK(32, 64) PICK(64, 64) PICK(64, 128) PICK(128, 128) PICK(16, 32) PICK(32, 32)
 #undef PICK
   return sprout_fail("multimap_attention_mma: no kernel for these sizes");

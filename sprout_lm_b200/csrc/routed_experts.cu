@@ -12,7 +12,7 @@
 //                  rows = W_down act, f(g, u) = g' sigmoid(alpha g') (u' + 1), g' = min(g, limit),
 //                  u' = clamp(u, -limit, limit).
 //  * moe_up / moe_down (mma):   the same two products on tensor cores (bfloat16, `mma.sync.m16n8k16`, float32
-//                  accumulation): a CTA makes 128 arranged rows of one expert x 128 columns, K in steps of 32
+//                  accumulation): a CTA makes 128 arranged rows of one expert x 128 columns, K in steps of 64
 //                  through a three-stage cp.async ring; the tile list follows the experts' row counts on the
 //                  device.  In the up product a tile holds 64 gate columns and the 64 up columns that go with
 //                  them, so the activation is applied to the accumulators.
@@ -210,7 +210,7 @@ moe_down_plain_kernel(const T* __restrict__ act, const int* __restrict__ offsets
 
 
 // ------------------------------------------------------------------------------------------ tensor cores
-constexpr int GM = 128, GN = 128, GK = 32, GSTRIDE = GK + 8, GSTAGES = 3, GTHREADS = 256;
+constexpr int GM = 128, GN = 128, GK = 64, GSTRIDE = GK + 8, GSTAGES = 3, GTHREADS = 256;
 constexpr int GEMM_SMEM = GSTAGES * (GM + GN) * GSTRIDE * (int)sizeof(__nv_bfloat16);
 
 // The CTA's tile: expert and first row, from the experts' offsets.  False: no such tile.
@@ -257,8 +257,8 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ a, int a_stride, const int
   auto load = [&](int stage, int k0) {
     Tile at = As(stage), wt = Ws(stage);
 #pragma unroll
-    for (int i = 0; i < 2; i++) {
-      const int idx = tid + i * GTHREADS, row = idx >> 2, c = (idx & 3) * 8;
+    for (int i = 0; i < GM * (GK / 8) / GTHREADS; i++) {
+      const int idx = tid + i * GTHREADS, row = idx / (GK / 8), c = (idx % (GK / 8)) * 8;
       const bool in_k = k0 + c < K;
       const __nv_bfloat16* src = a_rows[row];
       if (src && in_k) cp_async16(&at[row][c], src + k0 + c);

@@ -69,7 +69,7 @@ _SIGNATURES = {
     "sprout_glu_clamped": [_P, _P, _I, _I, _I, _F, _F, _P],
     "sprout_rope_maps_append": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_multimap_attention_simple": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _P, _P],
-    "sprout_multimap_attention_mma": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _P, _P],
+    "sprout_multimap_attention_mma": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _P, _P],
     "sprout_multimap_attention_mma_supported": [_I, _I, _I],
     "sprout_decay_chunks": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_decay_chunks_supported": [_I, _I, _I],
@@ -1288,7 +1288,8 @@ def multimap_attention(q, cache, ctx, out, heads: int, kv_heads: int, maps: int,
         _run("sprout_multimap_attention_mma", _ptr(q, "q"), q.stride(0), _ptr(k_cache, "k_cache"), _ptr(v_cache, "v_cache"),
              _ptr(cache.block_table, "block_table", torch.int32), cache.block_table.stride(0),
              _ptr(ctx.q_start, "q_start", torch.int32), _ptr(ctx.positions, "positions", torch.int32), _ptr(out, "out"),
-             out.stride(0), requests, tiles, heads, kv_heads, maps, dim, vdim, cache.page_tokens, k_cache.shape[0], float(scale),
+             out.stride(0), requests, tiles, int(getattr(ctx, "max_q_len", 0) or q.shape[0]), heads, kv_heads, maps, dim, vdim,
+             cache.page_tokens, k_cache.shape[0], float(scale),
              float(lam), float(norm_eps), float(out_scale), _ptr(status, "status", torch.int32), _stream())
         return
     multimap_attention_simple(q, cache, ctx, out, heads, kv_heads, maps, dim, vdim, scale, lam, norm_eps, out_scale, status)

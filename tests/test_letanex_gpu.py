@@ -127,30 +127,40 @@ def test_two_map_attention_over_pages(dtype, sizes):
     view, keys, values, status = _fill_cache(kernels, dtype, contexts, G, 2, dim, vdim, page, cos, sin, rng)
     scale, lam, eps, out_scale = 0.3, 0.37, 1e-5, 0.6
     tol = 3e-5 if dtype == "float32" else 3e-2
-    # the last min(n, 5) positions of every request are the step's queries
+    # the last few positions of every request are the step's queries: single tokens, short portions and long ones
+    wanted = [min(n, 5) for n in contexts]
+    wanted[0], wanted[-2], wanted[-1] = 1, 40, 100
     q_rows, positions, seqs = [], [], []
     for r, n in enumerate(contexts):
-        for p in range(max(0, n - 5), n):
+        for p in range(n - wanted[r], n):
             positions.append(p)
             seqs.append(r)
     q = rounded(rng.normal(0, 1.0, size=(len(positions), H, 2, dim)), dtype)
     rows = dev(q.reshape(len(positions), -1), dtype)
     kernels.rope_maps_append(rows, ints(positions), ints(seqs), view.block_table, cos, sin, None, None, H * 2, G, 2, dim, vdim,
                              page, False, status)
-    starts = np.concatenate([[0], np.cumsum([min(n, 5) for n in contexts])])
-    ctx = SimpleNamespace(positions=ints(positions), seq_of_token=ints(seqs), q_start=ints(starts))
+    starts = np.concatenate([[0], np.cumsum(wanted)])
+    ctx = SimpleNamespace(positions=ints(positions), seq_of_token=ints(seqs), q_start=ints(starts), max_q_len=max(wanted))
     out = torch.empty(len(positions), H * vdim, dtype=DTYPES[dtype], device=DEV)
     kernels.multimap_attention(rows, view, ctx, out, H, G, 2, dim, vdim, scale, lam, eps, out_scale, status)
     got = out.float().cpu().numpy().reshape(len(positions), H, vdim)
+    # the same with single tokens only (every request's last position): the step a decoding batch makes
+    last = [int(starts[r + 1]) - 1 for r in range(len(contexts))]
+    single = SimpleNamespace(positions=ints([positions[i] for i in last]), seq_of_token=ints(range(len(contexts))),
+                             q_start=ints(range(len(contexts) + 1)), max_q_len=1)
+    out1 = torch.empty(len(contexts), H * vdim, dtype=DTYPES[dtype], device=DEV)
+    kernels.multimap_attention(rows[last].contiguous(), view, single, out1, H, G, 2, dim, vdim, scale, lam, eps, out_scale, status)
+    got1 = out1.float().cpu().numpy().reshape(len(contexts), H, vdim)
     assert int(status.item()) == 0
     at = 0
     for r, n in enumerate(contexts):
-        count = min(n, 5)
+        count = wanted[r]
         pos = list(range(n - count, n))
         qr = plain.rotate(q[at:at + count].numpy().astype(np.float64).reshape(count, H * 2, dim), pos, rot_spec).reshape(count, H, 2, dim)
         kr = plain.rotate(keys[r].reshape(n, G * 2, dim), list(range(n)), rot_spec).reshape(n, G, 2, dim)
         want = plain.differential_heads(qr, kr, values[r], pos, scale, lam, eps, out_scale)
         assert np.abs(got[at:at + count] - want).max() <= tol, (n, np.abs(got[at:at + count] - want).max())
+        assert np.abs(got1[r] - want[-1]).max() <= tol, (n, "single token", np.abs(got1[r] - want[-1]).max())
         at += count
 
 
