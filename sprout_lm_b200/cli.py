@@ -1,8 +1,8 @@
 """Command line in the manner of the reference's demo (src/demo.ts) and smoke script
 (scripts/smoke-cuda.ts).
 
-    python -m sprout_lm_b200 demo [--model DIR | --tiny A|B|T] [--seed S] [--json] [--pressure] [--dtype bfloat16|float32]
-    python -m sprout_lm_b200 generate (--model DIR | --tiny A|B|T) --prompt 1,2,3 [--max-new-tokens N]
+    python -m sprout_lm_b200 demo [--model DIR | --tiny A|B|T|L] [--seed S] [--json] [--pressure] [--dtype bfloat16|float32]
+    python -m sprout_lm_b200 generate (--model DIR | --tiny A|B|T|L) --prompt 1,2,3 [--max-new-tokens N]
                                       [--temperature T] [--seed S] [--ignore-eos] [--json]
     python -m sprout_lm_b200 random-model --out DIR --config CONFIG.json [--seed S]
 
@@ -52,6 +52,25 @@ TINY_CONFIGS = {
                      _latent_layer("latent_attention_2", 4, 16, 16, 24, 64, 10000.0, 256, kv_from=0),
                      _latent_layer("latent_attention", 2, 32, 16, 32, 48, 50000.0, 192, q_rank=64)]},
 }
+
+
+# --tiny L: a tiny random Letanex model (attention with two maps per head, a layer that reads the first one's keys and
+# values, linear attention with decay and a state per request, a dense and two routed feed-forwards)
+def _routed(experts, identity, top, ff, shared):
+    return {"kind": "moe", "router": {"experts": experts, "identity": identity, "top": top, "scale": 1.0},
+            "expert": {"ff": ff, "limit": 4.0}, "shared": {"ff": shared, "limit": 4.0}}
+
+
+def _two_maps(heads, kv_heads, dim, vdim, **extra):
+    return {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "diff": 0.4,
+            "rot": {"base": 10000.0, "dims": dim // 2, "scaling": {"factor": 2.0}}, **extra}
+
+
+TINY_CONFIGS["L"] = {
+    "architecture": "Letanex", "vocab": 384, "width": 128, "norm": {"eps": 1e-5}, "max_positions": 512,
+    "layers": [{"type": "attention", "mixer": _two_maps(4, 2, 16, 32), "mlp": {"kind": "dense", "ff": 256}},
+               {"type": "lightning", "mixer": {"heads": 2, "dim": 64, "vdim": 32, "decay": [0.9, 0.99]}, "mlp": _routed(6, 2, 2, 64, 96)},
+               {"type": "attention", "mixer": _two_maps(4, 2, 16, 32, kv_from=0), "mlp": _routed(6, 2, 2, 64, 96)}]}
 
 
 def _table(rows: list[dict]) -> str:
@@ -201,7 +220,7 @@ def main(argv=None) -> int:
         p.add_argument("--model", help="folder with config.json and model.safetensors")
         p.add_argument("--tiny", choices=sorted(TINY) + sorted(TINY_CONFIGS), help="instead of --model: a tiny random model (A: 2 layers, "
                        "hidden 64, 4/2 heads of 16, tied head; B: 3 layers, hidden 96, 3/1 heads of 32, untied head; T: a Tulipel "
-                       "model of 4 latent-attention layers, width 128), written with --seed")
+                       "model of 4 latent-attention layers, width 128; L: a Letanex model of 3 layers, width 128), written with --seed")
         p.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
         p.add_argument("--seed", type=int, default=0)
     rnd = sub.add_parser("random-model", help="write config.json and model.safetensors with random weights")
