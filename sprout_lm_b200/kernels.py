@@ -71,7 +71,7 @@ _SIGNATURES = {
     "sprout_multimap_attention_simple": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _P, _P],
     "sprout_multimap_attention_mma": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _P, _P],
     "sprout_multimap_attention_mma_supported": [_I, _I, _I],
-    "sprout_decay_chunks": [_P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
+    "sprout_decay_chunks": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "sprout_decay_chunks_supported": [_I, _I, _I],
     "sprout_decay_scan": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "sprout_moe_route": [_P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
@@ -1301,7 +1301,8 @@ CHUNKED_FROM = 8            # a step whose longest portion has at least this man
 def decay_attention(rows, ctx, state, decay, out, heads: int, dim: int, vdim: int, silu: bool, status):
     """Linear attention with decay over the step's tokens, from and into the requests' state slots: prompt portions
     of bfloat16 rows run 64 tokens at a time on tensor cores when the key size is one the kernel is built for
-    (``SPROUT_DECAY_ATTENTION=scan`` keeps the token-by-token kernel), everything else token by token in float32.
+    (``SPROUT_DECAY_ATTENTION=scan`` keeps the token-by-token kernel, ``=chain`` the form in which a CTA walks its
+    request's chunks in order), everything else token by token in float32.
     The chunked path replaces q, k and v in ``rows`` by their activation."""
     if rows.dtype == torch.bfloat16 and getattr(ctx, "max_q_len", 1) >= CHUNKED_FROM and os.environ.get("SPROUT_DECAY_ATTENTION", "chunks") != "scan" \
             and rows.stride(1) == 1 and rows.data_ptr() % 16 == 0 \
@@ -1312,13 +1313,20 @@ def decay_attention(rows, ctx, state, decay, out, heads: int, dim: int, vdim: in
             raise KernelError("decay_attention: state must be contiguous float32 [slots, heads, dim, vdim]")
         if not out.is_contiguous() or tuple(out.shape) != (rows.shape[0], heads * vdim) or decay.numel() != heads:
             raise KernelError("decay_attention: out must be contiguous float32 [tokens, heads * vdim], one decay per head")
+        global LAUNCHES
+        requests = state.slots.numel()
+        sums, max_chunks = None, 0
+        if os.environ.get("SPROUT_DECAY_ATTENTION", "chunks") != "chain":
+            # all chunks at once: scratch for every chunk's own sums, which the scan turns into the state before the chunk
+            max_chunks = rows.shape[0] // 64 + requests
+            sums = torch.empty((max_chunks, heads, dim, vdim), dtype=torch.float32, device=rows.device)
+            LAUNCHES += 2
         _run("sprout_decay_chunks", _ptr(rows, "rows"), rows.stride(0), _ptr(ctx.q_start, "q_start", torch.int32),
              _ptr(state.slots, "state_slots", torch.int32), _ptr(buffer, "state", torch.float32), buffer.shape[0],
-             _ptr(decay, "decay", torch.float32), _ptr(out, "out", torch.float32), rows.shape[0], state.slots.numel(), heads,
-             dim, vdim, 1 if silu else 0, _ptr(status, "status", torch.int32), _stream())
+             _ptr(decay, "decay", torch.float32), _ptr(out, "out", torch.float32), _ptr(sums, "sums", torch.float32, True),
+             max_chunks, rows.shape[0], requests, heads, dim, vdim, 1 if silu else 0, _ptr(status, "status", torch.int32), _stream())
         if silu:
-            global LAUNCHES
-            LAUNCHES += 1           # the activation pass and the chunks behind one call
+            LAUNCHES += 1           # the activation pass behind the same call
         return
     decay_scan(rows, ctx.q_start, state.slots, state.buffer, decay, out, heads, dim, vdim, silu, status)
 
