@@ -58,8 +58,8 @@ def _parse_mixer(index: int, kind: str, m: Mapping) -> dict:
            "vdim": _positive_int(m, "vdim", where)}
     if kind == "lightning":
         decay = m.get("decay")
-        if not isinstance(decay, list) or len(decay) != out["heads"] or not all(_number(d) and 0 < d <= 1 for d in decay):
-            raise ConfigError(f"Invalid Letanex config: {where}.decay must list one number in (0, 1] per head.")
+        if not isinstance(decay, list) or len(decay) != out["heads"] or not all(_number(d) and d >= 0 for d in decay):
+            raise ConfigError(f"Invalid Letanex config: {where}.decay must list one non-negative number per head.")
         out["decay"] = [float(d) for d in decay]
         return out
     out["kv_heads"] = _positive_int(m, "kv_heads", where)

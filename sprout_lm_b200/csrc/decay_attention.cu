@@ -11,7 +11,7 @@
 //                 chunk and S the state before it,
 //                   o_i = sum_{j <= i} decay^(i-j) (q_i . k_j) v_j + decay^(i+1) q_i^T S,
 //                   S  <- decay^n S + sum_j (decay^(n-1-j) k_j) v_j^T.
-//                 A CTA owns (request, head, 32 value columns) and keeps its part of S in accumulator registers
+//                 A CTA owns (request, head, 64 value columns) and keeps its part of S in accumulator registers
 //                 (float32) from chunk to chunk.  What enters the recurrence stays 32-bit in effect: the decayed keys
 //                 and the state read by the queries go to the tensor cores as two bfloat16 terms each (value = high +
 //                 low), so their rounding is 2^-17, not 2^-9; the decay powers are float32.  Two forms: a CTA walking its
@@ -79,7 +79,7 @@ decay_scan_kernel(const T* __restrict__ rows, int row_stride, const int* __restr
 
 
 // ------------------------------------------------------------------------------------------ tensor cores
-constexpr int DC = 64, DVB = 32, DC_THREADS = 128;     // tokens per chunk, value columns per CTA
+constexpr int DC = 64, DVB = 64, DC_THREADS = 128;     // tokens per chunk, value columns per CTA
 
 // q, k, v of a row in place: act(x) as bfloat16 holds it (the chunked kernels then copy tiles as they are); 8 elements a thread
 __global__ void silu_rows_kernel(__nv_bfloat16* __restrict__ rows, int row_stride, int width8, long long count8) {

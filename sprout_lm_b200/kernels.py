@@ -1298,13 +1298,14 @@ def multimap_attention(q, cache, ctx, out, heads: int, kv_heads: int, maps: int,
 CHUNKED_FROM = 8            # a step whose longest portion has at least this many tokens runs the chunked decay kernel
 
 
-def decay_attention(rows, ctx, state, decay, out, heads: int, dim: int, vdim: int, silu: bool, status):
+def decay_attention(rows, ctx, state, decay, out, heads: int, dim: int, vdim: int, silu: bool, status, chunked: bool = True):
     """Linear attention with decay over the step's tokens, from and into the requests' state slots: prompt portions
     of bfloat16 rows run 64 tokens at a time on tensor cores when the key size is one the kernel is built for
     (``SPROUT_DECAY_ATTENTION=scan`` keeps the token-by-token kernel, ``=chain`` the form in which a CTA walks its
     request's chunks in order), everything else token by token in float32.
-    The chunked path replaces q, k and v in ``rows`` by their activation."""
-    if rows.dtype == torch.bfloat16 and getattr(ctx, "max_q_len", 1) >= CHUNKED_FROM and os.environ.get("SPROUT_DECAY_ATTENTION", "chunks") != "scan" \
+    The chunked path replaces q, k and v in ``rows`` by their activation; ``chunked=False`` (decays outside (0, 1],
+    whose powers it could not take) keeps the token-by-token kernel."""
+    if chunked and rows.dtype == torch.bfloat16 and getattr(ctx, "max_q_len", 1) >= CHUNKED_FROM and os.environ.get("SPROUT_DECAY_ATTENTION", "chunks") != "scan" \
             and rows.stride(1) == 1 and rows.data_ptr() % 16 == 0 \
             and (_lib or load_library()).sprout_decay_chunks_supported(dim, vdim, rows.stride(0)):
         _rows_contiguous(rows, "rows")

@@ -28,6 +28,8 @@ class DecayLinearAttention(Part):
             raise ValueError("decay_linear_attention: activation must be 'silu' or 'none'")
         self.hidden_size, self.heads, self.dim, self.value_dim = hidden_size, heads, dim, value_dim
         self.decay_values, self.eps, self.silu = decay, float(eps), activation == "silu"
+        # the chunked kernel takes powers of the decays (through their logarithms): decays in (0, 1] only
+        self.chunkable = all(0.0 < d <= 1.0 for d in decay)
         self.names = {key: prefix + value for key, value in {**DEFAULT_NAMES, **(names or {})}.items()}
         self.runtime = None
 
@@ -60,7 +62,7 @@ class DecayLinearAttention(Part):
         width = self.heads * self.value_dim
         o = torch.empty((rows.shape[0], width), dtype=torch.float32, device=rows.device)
         kernels.decay_attention(rows, ctx, state, self.decay, o, self.heads, self.dim, self.value_dim, self.silu,
-                                self.runtime.status)
+                                self.runtime.status, chunked=self.chunkable)
         gated = torch.empty((rows.shape[0], width), dtype=rows.dtype, device=rows.device)
         kernels.gated_rmsnorm(o, self.gain, rows[:, rows.shape[1] - width:], gated, self.eps)
         self.out.forward(gated, residual=x)

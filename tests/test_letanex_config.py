@@ -57,6 +57,7 @@ def test_model_spec_follows_the_file():
     (lambda c: c["layers"][2]["mixer"].__setitem__("kv_from", 3), "kv_from"),
     (lambda c: c["layers"][2]["mixer"].__setitem__("vdim", 16), "kv_from"),
     (lambda c: c["layers"][0]["mixer"].__setitem__("decay", [0.5, 0.5]), "decay"),
+    (lambda c: c["layers"][0]["mixer"].__setitem__("decay", [0.5, -0.1, 0.5]), "decay"),
     (lambda c: c["layers"][0]["mlp"]["router"].__setitem__("top", 9), "top"),
     (lambda c: c["layers"][0]["mlp"].pop("expert"), "expert"),
     (lambda c: c["layers"][0].__setitem__("type", "window"), "type"),
