@@ -197,6 +197,9 @@ struct MultiMapParams {
   int requests, heads, kv_heads, page_tokens, num_pages;
   float scale, lambda, norm_eps, out_scale;
   int* status;
+  // single-token steps may divide a request's tiles among `ksplit` CTAs (blockIdx.z); each then leaves its maxima, sums
+  // and unnormalised accumulators in `partial` [requests, kv_heads, ksplit, 16 rows, maps, 2 + vdim] for the merge kernel
+  int ksplit; float* partial;
 };
 
 template <int DIM, int VDIM, int MAPS, bool SPLIT>
@@ -276,9 +279,10 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
       else *(uint4*)dst = make_uint4(0, 0, 0, 0);
     }
   };
-  find_rows(0, 0);
+  const int first_tile = SPLIT ? (int)blockIdx.z : 0, tile_step = SPLIT ? p.ksplit : 1;    // this CTA's tiles: every tile_step-th
+  if (first_tile < kv_tiles) find_rows(first_tile, 0);
   __syncthreads();
-  load_tile(0);
+  if (first_tile < kv_tiles) load_tile(0);
   cp_async_commit();
 
   // SPLIT (a step in which no request has more than 16 rows: single tokens, the heads of one key/value group): a CTA
@@ -302,11 +306,12 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
   const float scale_log2 = p.scale * 1.4426950408889634f;
   const int warp_min_limit = s_limit[min(qrow, last_row)];
 
-  for (int t = 0; t < kv_tiles; t++) {
-    const int buf = t & 1;
-    if (t + 1 < kv_tiles) find_rows(t + 1, buf ^ 1);
+  int buf = 1;
+  for (int t = first_tile; t < kv_tiles; t += tile_step) {
+    buf ^= 1;
+    if (t + tile_step < kv_tiles) find_rows(t + tile_step, buf ^ 1);
     __syncthreads();                                   // rows visible; everyone is done with buffer buf ^ 1
-    if (t + 1 < kv_tiles) load_tile(buf ^ 1);
+    if (t + tile_step < kv_tiles) load_tile(buf ^ 1);
     cp_async_commit();
     cp_async_wait<1>();                                // tile t (and Q) have landed
     __syncthreads();
@@ -423,6 +428,8 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
         top1 = fmaxf(top1, at[1]);
       }
       l0[m] = l1[m] = 0.f;
+      m0[m] = top0;
+      m1[m] = top1;
 #pragma unroll
       for (int i = 0; i < VDIM / 8; i++) o[m][i][0] = o[m][i][1] = o[m][i][2] = o[m][i][3] = 0.f;
       for (int w = 0; w < MM_THREADS / 32; w++) {
@@ -440,6 +447,22 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
         }
       }
     }
+  }
+  if (SPLIT && p.ksplit > 1) {
+    // this CTA saw a share of the keys: what it has goes to the merge kernel
+    float* base = p.partial + ((((size_t)r * p.kv_heads + g) * p.ksplit + blockIdx.z) * 16) * MAPS * (2 + VDIM);
+#pragma unroll
+    for (int m = 0; m < MAPS; m++) {
+      float* row0 = base + ((size_t)my_row0 * MAPS + m) * (2 + VDIM);
+      float* row1 = base + ((size_t)my_row1 * MAPS + m) * (2 + VDIM);
+      if (qc == 0) { row0[0] = m0[m]; row0[1] = l0[m]; row1[0] = m1[m]; row1[1] = l1[m]; }
+#pragma unroll
+      for (int i = 0; i < VDIM / 8; i++) {
+        *(float2*)(row0 + 2 + i * 8 + qc * 2) = make_float2(o[m][i][0], o[m][i][1]);
+        *(float2*)(row1 + 2 + i * 8 + qc * 2) = make_float2(o[m][i][2], o[m][i][3]);
+      }
+    }
+    return;
   }
 #pragma unroll
   for (int m = 0; m < MAPS; m++) {
@@ -481,6 +504,49 @@ multimap_attention_mma_kernel(const MultiMapParams p) {
   }
 }
 
+// One block per (request, key/value head, row): the CTAs' shares of a request's keys into the head's output.
+template <int MAPS>
+__global__ void __launch_bounds__(128)
+multimap_merge_kernel(const MultiMapParams p, int vdim) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x, g = blockIdx.y, row = blockIdx.z, group = p.heads / p.kv_heads;
+  const int q0 = p.q_start[r], rows_total = (p.q_start[r + 1] - q0) * group;
+  if (row >= rows_total) return;
+  const int token = q0 + row / group, head = g * group + row % group;
+  const float scale_log2 = p.scale * 1.4426950408889634f;
+  const float* base = p.partial + (((size_t)r * p.kv_heads + g) * p.ksplit * 16 + row) * MAPS * (2 + vdim);
+  const size_t share = (size_t)16 * MAPS * (2 + vdim);
+  float v[2] = {0.f, 0.f};                             // columns threadIdx.x and threadIdx.x + 128
+#pragma unroll
+  for (int m = 0; m < MAPS; m++) {
+    float top = -INFINITY;
+    for (int z = 0; z < p.ksplit; z++) top = fmaxf(top, base[z * share + m * (2 + vdim)]);
+    float sum = 0.f, a[2] = {0.f, 0.f};
+    for (int z = 0; z < p.ksplit; z++) {
+      const float* at = base + z * share + m * (2 + vdim);
+      const float f = at[0] == -INFINITY ? 0.f : exp2f((at[0] - top) * scale_log2);
+      sum = fmaf(at[1], f, sum);
+#pragma unroll
+      for (int part = 0; part < 2; part++)
+        if (threadIdx.x + part * 128 < vdim) a[part] = fmaf(at[2 + threadIdx.x + part * 128], f, a[part]);
+    }
+#pragma unroll
+    for (int part = 0; part < 2; part++) v[part] += (m == 0 ? 1.0f : -p.lambda) * (a[part] / sum);
+  }
+  float squares = 0.f;
+#pragma unroll
+  for (int part = 0; part < 2; part++)
+    if (threadIdx.x + part * 128 < vdim) squares = fmaf(v[part], v[part], squares);
+  float factor = p.out_scale;
+  if (p.norm_eps > 0.f) factor *= 1.0f / sqrtf(block_sum(squares, scratch) / (float)vdim + p.norm_eps);
+  __nv_bfloat16* dst = p.out + (size_t)token * p.out_stride + (size_t)head * vdim;
+#pragma unroll
+  for (int part = 0; part < 2; part++)
+    if (threadIdx.x + part * 128 < vdim) dst[threadIdx.x + part * 128] = __float2bfloat16_rn(v[part] * factor);
+}
+
 template <int DIM, int VDIM, int MAPS, bool SPLIT>
 int launch_multimap(const MultiMapParams& p, int grid_x, cudaStream_t stream) {
   const int tiles_bytes = (3 * MM_ROWS * (MAPS * DIM + 8) + 2 * MM_KEYS * (VDIM + 8)) * 2;
@@ -492,8 +558,14 @@ int launch_multimap(const MultiMapParams& p, int grid_x, cudaStream_t stream) {
     if (err != cudaSuccess) return sprout_fail("multimap_attention_mma: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(err));
     configured = true;
   }
-  sprout_launch(multimap_attention_mma_kernel<DIM, VDIM, MAPS, SPLIT>, dim3(grid_x, p.kv_heads), dim3(MM_THREADS), smem, stream, p);
-  return sprout_check_launch("multimap_attention_mma");
+  sprout_launch(multimap_attention_mma_kernel<DIM, VDIM, MAPS, SPLIT>, dim3(grid_x, p.kv_heads, SPLIT ? p.ksplit : 1), dim3(MM_THREADS),
+                smem, stream, p);
+  if (int code = sprout_check_launch("multimap_attention_mma")) return code;
+  if (SPLIT && p.ksplit > 1) {
+    sprout_launch(multimap_merge_kernel<MAPS>, dim3(p.requests, p.kv_heads, 16), dim3(128), 0, stream, p, VDIM);
+    return sprout_check_launch("multimap_merge");
+  }
+  return 0;
 }
 
 bool mma_sizes(int maps, int dim, int vdim) {
@@ -505,6 +577,11 @@ bool mma_sizes(int maps, int dim, int vdim) {
 
 SPROUT_API int sprout_multimap_attention_mma_supported(int maps, int dim, int vdim) { return mma_sizes(maps, dim, vdim) ? 1 : 0; }
 
+// Floats of scratch that a step of single tokens needs when a request's keys are divided among `ksplit` CTAs.
+SPROUT_API long long sprout_multimap_partial_floats(int requests, int kv_heads, int maps, int vdim, int ksplit) {
+  return (long long)requests * kv_heads * ksplit * 16 * maps * (2 + vdim);
+}
+
 // bfloat16 only.  `tiles` bounds the (request, 64 rows) tiles of the batch: sum over requests of
 // ceil(tokens * heads / kv_heads / 64), or any larger number; `max_q_len` is the most tokens any request brings.
 SPROUT_API int sprout_multimap_attention_mma(const void* q, int q_stride, const void* k_cache, const void* v_cache,
@@ -512,7 +589,7 @@ SPROUT_API int sprout_multimap_attention_mma(const void* q, int q_stride, const 
                                              const int* positions, void* out, int out_stride, int requests, int tiles,
                                              int max_q_len, int heads, int kv_heads, int maps, int dim, int vdim, int page_tokens,
                                              int num_pages, float scale, float lambda, float norm_eps, float out_scale,
-                                             int* status, cudaStream_t stream) {
+                                             int ksplit, float* partial, int* status, cudaStream_t stream) {
   SPROUT_REQUIRE(q && k_cache && v_cache && block_table && q_start && positions && out && status, "multimap_attention_mma: null pointer");
   SPROUT_REQUIRE(requests > 0 && tiles > 0 && max_q_len > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && page_tokens > 0 &&
                  num_pages > 0, "multimap_attention_mma: bad sizes");
@@ -522,7 +599,9 @@ SPROUT_API int sprout_multimap_attention_mma(const void* q, int q_stride, const 
   SPROUT_REQUIRE(kv_heads <= 65535, "multimap_attention_mma: too many key/value heads");
   MultiMapParams p{(const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
                    table_stride, q_start, positions, (__nv_bfloat16*)out, out_stride, requests, heads, kv_heads, page_tokens,
-                   num_pages, scale, lambda, norm_eps, out_scale, status};
+                   num_pages, scale, lambda, norm_eps, out_scale, status, ksplit, partial};
+  SPROUT_REQUIRE(ksplit >= 1 && ksplit <= 64 && (ksplit == 1 || (partial && max_q_len * (heads / kv_heads) <= 16)),
+                 "multimap_attention_mma: keys are divided among CTAs in single-token steps only, with scratch for the shares");
   const bool split = max_q_len * (heads / kv_heads) <= 16;
 #define PICK(D, V)                                                                                              \
   if (dim == D && vdim == V) {                                                                                  \

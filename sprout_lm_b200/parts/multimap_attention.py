@@ -54,6 +54,10 @@ class MultiMapAttention(Part):
     def state_spec(self):
         return None
 
+    def decode_plan(self, requests: int, max_keys: int, planned_context: int, page_tokens: int):
+        """Into how many CTAs a step of one token per request divides a request's keys: it follows the contexts' length."""
+        return kernels.multimap_key_split(requests, self.kv_heads, self.heads // self.kv_heads, 1, planned_context)
+
     def tensor_decls(self):
         n = self.names
         decls = [TensorDecl(n["q"], (self.q_width, self.hidden_size))]

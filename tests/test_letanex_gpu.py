@@ -144,10 +144,11 @@ def test_two_map_attention_over_pages(dtype, sizes):
     out = torch.empty(len(positions), H * vdim, dtype=DTYPES[dtype], device=DEV)
     kernels.multimap_attention(rows, view, ctx, out, H, G, 2, dim, vdim, scale, lam, eps, out_scale, status)
     got = out.float().cpu().numpy().reshape(len(positions), H, vdim)
-    # the same with single tokens only (every request's last position): the step a decoding batch makes
+    # the same with single tokens only (every request's last position): the step a decoding batch makes, in which
+    # the bfloat16 kernel divides a request's keys among several CTAs (some of which find no keys in the short requests)
     last = [int(starts[r + 1]) - 1 for r in range(len(contexts))]
     single = SimpleNamespace(positions=ints([positions[i] for i in last]), seq_of_token=ints(range(len(contexts))),
-                             q_start=ints(range(len(contexts) + 1)), max_q_len=1)
+                             q_start=ints(range(len(contexts) + 1)), max_q_len=1, max_context=max(contexts))
     out1 = torch.empty(len(contexts), H * vdim, dtype=DTYPES[dtype], device=DEV)
     kernels.multimap_attention(rows[last].contiguous(), view, single, out1, H, G, 2, dim, vdim, scale, lam, eps, out_scale, status)
     got1 = out1.float().cpu().numpy().reshape(len(contexts), H, vdim)
@@ -181,7 +182,7 @@ def test_attention_finds_a_far_key_and_ignores_the_future(dtype, dims):
     view, k, v, status = _fill_cache(kernels, dtype, [n], G, 2, dim, vdim, page, None, None, rng, keys=[keys], values=[values])
     q = np.zeros((1, H, 2, dim))
     q[0, 0, 0, 5] = 8.0                            # head 0, map 0 asks for the far key; the other maps are uniform
-    ctx = SimpleNamespace(positions=ints([query_at]), seq_of_token=ints([0]), q_start=ints([0, 1]))
+    ctx = SimpleNamespace(positions=ints([query_at]), seq_of_token=ints([0]), q_start=ints([0, 1]), max_q_len=1, max_context=n)
     out = torch.empty(1, H * vdim, dtype=DTYPES[dtype], device=DEV)
     kernels.multimap_attention(dev(q.reshape(1, -1).astype(np.float32), dtype), view, ctx, out, H, G, 2, dim, vdim, 1.0, 0.0, 0.0, 1.0, status)
     got = out.float().cpu().numpy().reshape(H, vdim)
