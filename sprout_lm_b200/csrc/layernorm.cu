@@ -6,8 +6,9 @@
 //                    sublayer in one launch.
 //  * gated_rmsnorm:  out = o / sqrt(mean(o^2) + eps) * w * sigmoid(gate).
 //  * relu2, glu_clamped: activations between the two products of a feed-forward.
-// One block per row; sums in a fixed order that depends on the block size alone, so a row's result
-// does not depend on what else is in the batch.
+// One block per row, or (rows of 128 to 4,096 elements in steps the kernels are built for) a warp per row with the row
+// in registers; sums in a fixed order that depends on the row's width alone, so a row's result does not depend on
+// what else is in the batch.
 #include "common.cuh"
 
 namespace {
@@ -70,6 +71,102 @@ norm_add_kernel(const float* __restrict__ y, const float* __restrict__ gain, flo
   for (int i = threadIdx.x; i < width; i += blockDim.x) h[at + i] = from_float<TO>((row[i] - mean) * rstd * next_gain[i]);
 }
 
+// ---- rows of 128 * NV elements: a warp per row, the row in registers, 16-byte accesses, no block-wide barrier
+template <typename TO>
+__device__ __forceinline__ void store_four(TO* dst, float a, float b, float c, float d) {
+  if (sizeof(TO) == 4) {
+    *(float4*)dst = make_float4(a, b, c, d);
+  } else {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    *(uint2*)dst = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+  }
+}
+
+template <int NV>
+__device__ __forceinline__ void warp_moments(const float4 (&v)[NV], float eps, float& mean, float& rstd) {
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; i++) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+  mean = warp_sum(s) / (float)(NV * 128);
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; i++) {
+    const float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, d = v[i].w - mean;
+    q += (a * a + b * b) + (c * c + d * d);
+  }
+  rstd = 1.0f / sqrtf(warp_sum(q) / (float)(NV * 128) + eps);
+}
+
+template <typename TO, int NV>
+__global__ void __launch_bounds__(128)
+layernorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gain, TO* __restrict__ out,
+                      const int* __restrict__ rows, int count, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= count) return;
+  const float4* src = (const float4*)(x + (size_t)(rows ? rows[row] : row) * (NV * 128));
+  float4 v[NV];
+#pragma unroll
+  for (int i = 0; i < NV; i++) v[i] = src[i * 32 + lane];
+  float mean, rstd;
+  warp_moments<NV>(v, eps, mean, rstd);
+  TO* dst = out + (size_t)row * (NV * 128);
+#pragma unroll
+  for (int i = 0; i < NV; i++) {
+    const float4 g = ((const float4*)gain)[i * 32 + lane];
+    store_four<TO>(dst + (i * 32 + lane) * 4, (v[i].x - mean) * rstd * g.x, (v[i].y - mean) * rstd * g.y, (v[i].z - mean) * rstd * g.z,
+                   (v[i].w - mean) * rstd * g.w);
+  }
+}
+
+template <typename TO, int NV>
+__global__ void __launch_bounds__(128)
+norm_add_rows_kernel(const float* __restrict__ y, const float* __restrict__ gain, float* __restrict__ x,
+                     const float* __restrict__ next_gain, TO* __restrict__ h, int count, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= count) return;
+  const size_t at = (size_t)row * (NV * 128);
+  float4 v[NV];
+#pragma unroll
+  for (int i = 0; i < NV; i++) v[i] = ((const float4*)(y + at))[i * 32 + lane];
+  float mean, rstd;
+  warp_moments<NV>(v, eps, mean, rstd);
+  float4* stream = (float4*)(x + at);
+#pragma unroll
+  for (int i = 0; i < NV; i++) {
+    const float4 g = ((const float4*)gain)[i * 32 + lane];
+    float4 s = stream[i * 32 + lane];
+    s.x += (v[i].x - mean) * rstd * g.x;
+    s.y += (v[i].y - mean) * rstd * g.y;
+    s.z += (v[i].z - mean) * rstd * g.z;
+    s.w += (v[i].w - mean) * rstd * g.w;
+    stream[i * 32 + lane] = s;
+    v[i] = s;
+  }
+  if (next_gain == nullptr) return;
+  warp_moments<NV>(v, eps, mean, rstd);
+#pragma unroll
+  for (int i = 0; i < NV; i++) {
+    const float4 g = ((const float4*)next_gain)[i * 32 + lane];
+    store_four<TO>(h + at + (i * 32 + lane) * 4, (v[i].x - mean) * rstd * g.x, (v[i].y - mean) * rstd * g.y, (v[i].z - mean) * rstd * g.z,
+                   (v[i].w - mean) * rstd * g.w);
+  }
+}
+
+// 0: no such kernel for the width
+inline int vectors_per_lane(int width) {
+  if (width % 128) return 0;
+  const int nv = width / 128;
+  return (nv == 1 || nv == 2 || nv == 4 || nv == 6 || nv == 8 || nv == 12 || nv == 16 || nv == 24 || nv == 32) ? nv : 0;
+}
+
+#define SPROUT_FOR_NV(nv, CALL) \
+  switch (nv) { case 1: CALL(1) break; case 2: CALL(2) break; case 4: CALL(4) break; case 6: CALL(6) break; case 8: CALL(8) break; \
+                case 12: CALL(12) break; case 16: CALL(16) break; case 24: CALL(24) break; default: CALL(32) break; }
+
 template <typename TG, typename TO>
 __global__ void __launch_bounds__(THREADS)
 gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ gain, const TG* __restrict__ gate,
@@ -124,6 +221,16 @@ SPROUT_API int sprout_layernorm(const float* x, const float* gain, void* out, in
                                 int width, float eps, cudaStream_t stream) {
   SPROUT_REQUIRE(x && gain && out && count > 0 && width > 0 && eps > 0, "layernorm: bad arguments");
   SPROUT_REQUIRE(width <= 40000, "layernorm: rows of up to 40000 elements (got %d)", width);
+  const int nv = vectors_per_lane(width);
+  if (nv && (out_dtype == SPROUT_F32 || out_dtype == SPROUT_BF16) && (((uintptr_t)x | (uintptr_t)gain | (uintptr_t)out) & 15) == 0) {
+    const dim3 grid((count + 3) / 4);
+#define CALL(N)                                                                                                                   \
+    if (out_dtype == SPROUT_F32) sprout_launch(layernorm_rows_kernel<float, N>, grid, dim3(128), 0, stream, x, gain, (float*)out, rows, count, eps); \
+    else sprout_launch(layernorm_rows_kernel<__nv_bfloat16, N>, grid, dim3(128), 0, stream, x, gain, (__nv_bfloat16*)out, rows, count, eps);
+    SPROUT_FOR_NV(nv, CALL)
+#undef CALL
+    return sprout_check_launch("layernorm_rows");
+  }
   const size_t smem = (size_t)(width + 34) * sizeof(float);
   if (out_dtype == SPROUT_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -143,6 +250,17 @@ SPROUT_API int sprout_norm_add(const float* y, const float* gain, float* x, cons
   SPROUT_REQUIRE(y && gain && x && count > 0 && width > 0 && eps > 0, "norm_add: bad arguments");
   SPROUT_REQUIRE((next_gain == nullptr) == (h == nullptr), "norm_add: the next norm's gain and its output go together");
   SPROUT_REQUIRE(width <= 40000, "norm_add: rows of up to 40000 elements (got %d)", width);
+  const int nv = vectors_per_lane(width);
+  if (nv && (h_dtype == SPROUT_F32 || h_dtype == SPROUT_BF16) &&
+      (((uintptr_t)y | (uintptr_t)gain | (uintptr_t)x | (uintptr_t)next_gain | (uintptr_t)h) & 15) == 0) {
+    const dim3 grid((count + 3) / 4);
+#define CALL(N)                                                                                                                   \
+    if (h_dtype == SPROUT_F32) sprout_launch(norm_add_rows_kernel<float, N>, grid, dim3(128), 0, stream, y, gain, x, next_gain, (float*)h, count, eps); \
+    else sprout_launch(norm_add_rows_kernel<__nv_bfloat16, N>, grid, dim3(128), 0, stream, y, gain, x, next_gain, (__nv_bfloat16*)h, count, eps);
+    SPROUT_FOR_NV(nv, CALL)
+#undef CALL
+    return sprout_check_launch("norm_add_rows");
+  }
   const size_t smem = (size_t)(width + 34) * sizeof(float);
   if (h_dtype == SPROUT_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(norm_add_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -38,7 +38,7 @@ def test_layernorm_and_norm_add(dtype):
     from sprout_lm_b200 import kernels
     rng = np.random.default_rng(0)
     tol = 2e-6 if dtype == "float32" else 2e-2
-    for width in (72, 257, 1030):
+    for width in (72, 257, 1030, 256, 768, 2048):                             # a block per row, and (the last three) a warp per row
         x = (rng.normal(3.0, 2.0, size=(6, width))).astype(np.float32)        # a mean far from zero: the deviations matter
         w, wb, w2 = (rng.normal(1.0, 0.3, size=width).astype(np.float32) for _ in range(3))
         out = torch.empty(6, width, dtype=DTYPES[dtype], device=DEV)
