@@ -16,6 +16,8 @@
 //                  through a three-stage cp.async ring; the tile list follows the experts' row counts on the
 //                  device.  In the up product a tile holds 64 gate columns and the 64 up columns that go with
 //                  them, so the activation is applied to the accumulators.
+//  * moe_few:      the same two products for steps of at most 8 tokens (bfloat16): a CTA per (expert, 32 output columns)
+//                  keeps the expert's few rows in shared memory and streams every weight row once for all of them.
 //  * moe_combine:  y[t] += sum over the token's places of weight * (identity ? h[t] : its row).
 #include "attention_bf16.cuh"
 
@@ -349,6 +351,77 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ a, int a_stride, const int
     }
 }
 
+// ------------------------------------------------------------------------------------------ a handful of tokens
+// With at most FEW tokens in the step no expert has more than FEW rows.  A CTA takes (expert, block of output columns),
+// keeps the expert's rows in shared memory and streams each weight row once with 16-byte loads for all of them: a warp
+// per output column, eight elements a lane and step, float32 sums added across the lanes in a fixed order.
+constexpr int FEW = 8, FEW_COLS = 32;
+
+template <bool UP>
+__global__ void __launch_bounds__(256)
+moe_few_kernel(const __nv_bfloat16* __restrict__ a, int a_stride, const int* __restrict__ order, const int* __restrict__ offsets,
+               const __nv_bfloat16* __restrict__ w, void* __restrict__ out, int top, int N, int K, float limit, float alpha) {
+  extern __shared__ __align__(16) unsigned char few_smem[];
+  __nv_bfloat16* rows = (__nv_bfloat16*)few_smem;            // FEW x K
+  pdl_launch_dependents();
+  pdl_wait();
+  const int e = blockIdx.x, row0 = offsets[e], count = min(offsets[e + 1] - row0, FEW);
+  if (count <= 0) return;
+  const int chunks = K / 8;
+  for (int idx = threadIdx.x; idx < count * chunks; idx += blockDim.x) {
+    const int r = idx / chunks, c = idx % chunks;
+    const __nv_bfloat16* src = UP ? a + (size_t)(order[row0 + r] / top) * a_stride : a + (size_t)(row0 + r) * a_stride;
+    *(uint4*)(rows + (size_t)r * K + c * 8) = *(const uint4*)(src + c * 8);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const __nv_bfloat16* wexp = w + (size_t)e * (UP ? 2 * N : N) * K;
+  for (int j = blockIdx.y * FEW_COLS + warp; j < min(N, (blockIdx.y + 1) * FEW_COLS); j += 8) {
+    const __nv_bfloat16* w0 = wexp + (size_t)j * K;
+    const __nv_bfloat16* w1 = wexp + (size_t)(N + j) * K;     // UP: the up row that goes with gate row j
+    float s0[FEW], s1[FEW];
+#pragma unroll
+    for (int r = 0; r < FEW; r++) s0[r] = s1[r] = 0.f;
+    for (int c = lane; c < chunks; c += 32) {
+      const uint4 g = *(const uint4*)(w0 + c * 8);
+      uint4 u = make_uint4(0, 0, 0, 0);
+      if (UP) u = *(const uint4*)(w1 + c * 8);
+      const __nv_bfloat162* gp = (const __nv_bfloat162*)&g;
+      const __nv_bfloat162* up = (const __nv_bfloat162*)&u;
+#pragma unroll
+      for (int r = 0; r < FEW; r++) {
+        if (r >= count) break;
+        const uint4 x = *(const uint4*)(rows + (size_t)r * K + c * 8);
+        const __nv_bfloat162* xp = (const __nv_bfloat162*)&x;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          const float2 xv = __bfloat1622float2(xp[i]), gv = __bfloat1622float2(gp[i]);
+          s0[r] = fmaf(xv.x, gv.x, s0[r]);
+          s0[r] = fmaf(xv.y, gv.y, s0[r]);
+          if (UP) {
+            const float2 uv = __bfloat1622float2(up[i]);
+            s1[r] = fmaf(xv.x, uv.x, s1[r]);
+            s1[r] = fmaf(xv.y, uv.y, s1[r]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < FEW; r++) {
+      if (r >= count) break;
+      const float g = warp_sum(s0[r]);
+      if (UP) {
+        const float u = warp_sum(s1[r]);
+        if (lane == 0)
+          ((__nv_bfloat16*)out)[(size_t)(row0 + r) * N + j] = __float2bfloat16_rn(
+              glu(__bfloat162float(__float2bfloat16_rn(g)), __bfloat162float(__float2bfloat16_rn(u)), limit, alpha));
+      } else if (lane == 0) {
+        ((float*)out)[(size_t)(row0 + r) * N + j] = g;
+      }
+    }
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(float* __restrict__ y, const T* __restrict__ h, int h_stride, const int* __restrict__ ids,
@@ -450,6 +523,21 @@ SPROUT_API int sprout_moe_experts_mma(const void* h, int h_stride, const int* or
                  "moe_experts_mma: sizes must be multiples of 8 (width %d, ff %d, row stride %d)", width, ff, h_stride);
   SPROUT_REQUIRE((((uintptr_t)h | (uintptr_t)w_gate_up | (uintptr_t)w_down | (uintptr_t)act | (uintptr_t)rows_out) & 15) == 0,
                  "moe_experts_mma: buffers must start on 16-byte boundaries");
+  if (entries <= FEW * top && (size_t)FEW * (width > ff ? width : ff) * 2 <= 160 * 1024) {
+    // at most FEW tokens: no expert has more rows than that, and the products are streams of weights
+    static bool few_prepared = false;
+    if (!few_prepared) {
+      cudaFuncSetAttribute(moe_few_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      cudaFuncSetAttribute(moe_few_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      few_prepared = true;
+    }
+    sprout_launch(moe_few_kernel<true>, dim3(experts, (ff + FEW_COLS - 1) / FEW_COLS), dim3(256), (size_t)FEW * width * 2, stream,
+                  (const __nv_bfloat16*)h, h_stride, order, offsets, (const __nv_bfloat16*)w_gate_up, act, top, ff, width, limit, alpha);
+    if (int code = sprout_check_launch("moe_up_few")) return code;
+    sprout_launch(moe_few_kernel<false>, dim3(experts, (width + FEW_COLS - 1) / FEW_COLS), dim3(256), (size_t)FEW * ff * 2, stream,
+                  (const __nv_bfloat16*)act, ff, order, offsets, (const __nv_bfloat16*)w_down, (void*)rows_out, top, width, ff, 0.f, 0.f);
+    return sprout_check_launch("moe_down_few");
+  }
   static bool prepared = false;
   if (!prepared) {
     cudaFuncSetAttribute(moe_gemm_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
