@@ -27,40 +27,49 @@ namespace {
 
 constexpr int ROUTE_THREADS = 256;
 
-// One block per token: the warps share the router's outputs (warp w takes outputs w, w + 8, ...), a lane sums every
-// 32nd element in four independent chains, the lanes are added in a fixed order; warp 0 then takes the softmax and the
-// choices.  Nothing depends on the other tokens of the batch.
-template <typename T>
+// A block takes ROUTE_TOKENS tokens (8 in steps of many tokens, 1 in steps of few, where blocks are scarce; a token's
+// sums are the same in both): the warps share the router's outputs (warp w takes outputs w, w + 8, ...) and apply every
+// weight they load to all 8 tokens; a lane sums every 32nd element, the lanes are added in a fixed order, so a token's
+// scores do not depend on the tokens beside it.  Warp t then takes token t's softmax and choices.
+template <typename T, int ROUTE_TOKENS>
 __global__ void __launch_bounds__(ROUTE_THREADS)
 moe_route_kernel(const T* __restrict__ h, int h_stride, const float* __restrict__ router, const float* __restrict__ correction,
                  int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ counts, int tokens, int width,
                  int outputs, int experts, int top, float scale) {
   extern __shared__ float smem[];
-  float* z = smem;                    // outputs: scores
-  float* choice = z + outputs;        // outputs
-  float* row = choice + outputs;      // width: the token's h as float32
+  float* zs = smem;                                   // ROUTE_TOKENS x outputs: scores
+  float* choices = zs + ROUTE_TOKENS * outputs;       // ROUTE_TOKENS x outputs
+  float* rows = choices + ROUTE_TOKENS * outputs;     // ROUTE_TOKENS x width: the tokens' h as float32
   pdl_launch_dependents();
   pdl_wait();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = blockIdx.x;
-  const T* src = h + (size_t)t * h_stride;
-  for (int k = threadIdx.x; k < width; k += ROUTE_THREADS) row[k] = to_float(src[k]);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t0 = blockIdx.x * ROUTE_TOKENS;
+  const int here = min(ROUTE_TOKENS, tokens - t0);
+  for (int i = threadIdx.x; i < ROUTE_TOKENS * width; i += ROUTE_THREADS) {
+    const int r = i / width, k = i % width;
+    rows[i] = r < here ? to_float(h[(size_t)(t0 + r) * h_stride + k]) : 0.f;
+  }
   __syncthreads();
   for (int e = warp; e < outputs; e += ROUTE_THREADS / 32) {
     const float* w = router + (size_t)e * width;
-    float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
-    int k = lane;
-    for (; k + 96 < width; k += 128) {
-      d0 = fmaf(row[k], w[k], d0);
-      d1 = fmaf(row[k + 32], w[k + 32], d1);
-      d2 = fmaf(row[k + 64], w[k + 64], d2);
-      d3 = fmaf(row[k + 96], w[k + 96], d3);
+    float dot[ROUTE_TOKENS];
+#pragma unroll
+    for (int r = 0; r < ROUTE_TOKENS; r++) dot[r] = 0.f;
+    for (int k = lane; k < width; k += 32) {
+      const float wk = w[k];
+#pragma unroll
+      for (int r = 0; r < ROUTE_TOKENS; r++) dot[r] = fmaf(rows[r * width + k], wk, dot[r]);
     }
-    for (; k < width; k += 32) d0 = fmaf(row[k], w[k], d0);
-    const float dot = warp_sum((d0 + d1) + (d2 + d3));
-    if (lane == 0) z[e] = dot;
+#pragma unroll
+    for (int r = 0; r < ROUTE_TOKENS; r++) {
+      const float sum = warp_sum(dot[r]);
+      if (lane == 0) zs[r * outputs + e] = sum;
+    }
   }
   __syncthreads();
-  if (warp != 0) return;
+  if (warp >= here) return;
+  const int t = t0 + warp;
+  float* z = zs + warp * outputs;
+  float* choice = choices + warp * outputs;
   float top_z = -INFINITY;
   for (int e = lane; e < outputs; e += 32) top_z = fmaxf(top_z, z[e]);
   top_z = warp_max(top_z);
@@ -449,17 +458,29 @@ SPROUT_API int sprout_moe_route(const void* h, int h_stride, int dtype, const fl
   SPROUT_REQUIRE(h && router && correction && ids && weights && counts, "moe_route: null pointer");
   SPROUT_REQUIRE(tokens > 0 && width > 0 && outputs > 0 && experts >= 0 && experts <= outputs && top > 0 && top <= outputs,
                  "moe_route: bad sizes (outputs %d, experts %d, top %d)", outputs, experts, top);
-  const size_t smem = (size_t)(2 * outputs + width) * sizeof(float);
-  SPROUT_REQUIRE(smem <= 48 * 1024, "moe_route: too many router outputs (%d) or too wide rows (%d)", outputs, width);
-  dim3 grid(tokens);
-  if (dtype == SPROUT_F32)
-    sprout_launch(moe_route_kernel<float>, grid, dim3(ROUTE_THREADS), smem, stream, (const float*)h, h_stride, router,
-                  correction, ids, weights, counts, tokens, width, outputs, experts, top, scale);
-  else if (dtype == SPROUT_BF16)
-    sprout_launch(moe_route_kernel<__nv_bfloat16>, grid, dim3(ROUTE_THREADS), smem, stream, (const __nv_bfloat16*)h, h_stride,
-                  router, correction, ids, weights, counts, tokens, width, outputs, experts, top, scale);
-  else
+  const int per_block = tokens > 64 ? 8 : 1;
+  const size_t smem = (size_t)per_block * (2 * outputs + width) * sizeof(float);
+  SPROUT_REQUIRE(smem <= 200 * 1024, "moe_route: too many router outputs (%d) or too wide rows (%d)", outputs, width);
+  static bool prepared = false;
+  if (!prepared) {
+    cudaFuncSetAttribute(moe_route_kernel<float, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(moe_route_kernel<float, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(moe_route_kernel<__nv_bfloat16, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(moe_route_kernel<__nv_bfloat16, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    prepared = true;
+  }
+  dim3 grid((tokens + per_block - 1) / per_block);
+#define ROUTE(T, N)                                                                                                    \
+  sprout_launch(moe_route_kernel<T, N>, grid, dim3(ROUTE_THREADS), smem, stream, (const T*)h, h_stride, router, correction, ids, \
+                weights, counts, tokens, width, outputs, experts, top, scale)
+  if (dtype == SPROUT_F32) {
+    if (per_block == 1) ROUTE(float, 1); else ROUTE(float, 8);
+  } else if (dtype == SPROUT_BF16) {
+    if (per_block == 1) ROUTE(__nv_bfloat16, 1); else ROUTE(__nv_bfloat16, 8);
+  } else {
     return sprout_fail("moe_route: unknown dtype %d", dtype);
+  }
+#undef ROUTE
   return sprout_check_launch("moe_route");
 }
 
