@@ -199,6 +199,12 @@ __global__ void relu2_kernel(const T* __restrict__ z, T* __restrict__ out, long 
 }
 
 // rows of [gate (ff) | up (ff)] -> g * sigmoid(alpha g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit)
+__device__ __forceinline__ float glu_value(float g, float u, float limit, float alpha) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+}
+
 template <typename T>
 __global__ void glu_clamped_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int ff, float limit, float alpha) {
   pdl_launch_dependents();
@@ -207,9 +213,29 @@ __global__ void glu_clamped_kernel(const T* __restrict__ gate_up, T* __restrict_
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
     const long long r = i / ff;
     const int j = (int)(i - r * ff);
-    const float g = fminf(to_float(gate_up[r * 2 * ff + j]), limit);
-    const float u = fminf(fmaxf(to_float(gate_up[r * 2 * ff + ff + j]), -limit), limit);
-    out[i] = from_float<T>(g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f));
+    out[i] = from_float<T>(glu_value(to_float(gate_up[r * 2 * ff + j]), to_float(gate_up[r * 2 * ff + ff + j]), limit, alpha));
+  }
+}
+
+// bfloat16 rows whose ff is a multiple of 8: eight elements a thread, 16-byte accesses
+__global__ void glu_clamped_vec_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int rows, int ff8,
+                                       float limit, float alpha) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long count = (long long)rows * ff8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / ff8;
+    const int j = (int)(i - r * ff8);
+    const uint4 g = ((const uint4*)gate_up)[r * 2 * ff8 + j], u = ((const uint4*)gate_up)[r * 2 * ff8 + ff8 + j];
+    const __nv_bfloat162* gp = (const __nv_bfloat162*)&g;
+    const __nv_bfloat162* up = (const __nv_bfloat162*)&u;
+    uint4 v;
+    __nv_bfloat162* vp = (__nv_bfloat162*)&v;
+#pragma unroll
+    for (int e = 0; e < 4; e++)
+      vp[e] = __floats2bfloat162_rn(glu_value(__low2float(gp[e]), __low2float(up[e]), limit, alpha),
+                                    glu_value(__high2float(gp[e]), __high2float(up[e]), limit, alpha));
+    ((uint4*)out)[i] = v;
   }
 }
 
@@ -308,6 +334,9 @@ SPROUT_API int sprout_glu_clamped(const void* gate_up, void* out, int dtype, int
   if (dtype == SPROUT_F32)
     sprout_launch(glu_clamped_kernel<float>, dim3(grid_for(count)), dim3(256), 0, stream, (const float*)gate_up, (float*)out,
                   rows, ff, limit, alpha);
+  else if (dtype == SPROUT_BF16 && ff % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0)
+    sprout_launch(glu_clamped_vec_kernel, dim3(grid_for(count / 8)), dim3(256), 0, stream, (const __nv_bfloat16*)gate_up,
+                  (__nv_bfloat16*)out, rows, ff / 8, limit, alpha);
   else if (dtype == SPROUT_BF16)
     sprout_launch(glu_clamped_kernel<__nv_bfloat16>, dim3(grid_for(count)), dim3(256), 0, stream,
                   (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows, ff, limit, alpha);
