@@ -27,6 +27,7 @@ using namespace sprout_attn;
 namespace {
 
 constexpr int CHUNK = 128;
+constexpr int PARTS = 4;     // value elements per thread in the float32-arithmetic kernel: vdim <= PARTS * CHUNK
 
 // Row of a token: [q: q_vectors * dim | k: kv_heads * maps * dim | v: kv_heads * vdim] (k and v only when `write`).
 template <typename T>
@@ -106,12 +107,13 @@ multimap_attention_simple_kernel(const T* __restrict__ q, int q_stride, const T*
   for (int d = tid; d < kw; d += CHUNK) qs[d] = to_float(q[(size_t)t * q_stride + (size_t)h * kw + d]);
   __syncthreads();
 
-  float m_run[MAPS], l_run[MAPS], acc[MAPS][2];
+  float m_run[MAPS], l_run[MAPS], acc[MAPS][PARTS];
 #pragma unroll
   for (int m = 0; m < MAPS; m++) {
     m_run[m] = -INFINITY;
     l_run[m] = 0.f;
-    acc[m][0] = acc[m][1] = 0.f;
+#pragma unroll
+    for (int part = 0; part < PARTS; part++) acc[m][part] = 0.f;
   }
   for (int base = 0; base <= pos; base += CHUNK) {
     const int p = base + tid;
@@ -152,7 +154,7 @@ multimap_attention_simple_kernel(const T* __restrict__ q, int q_stride, const T*
     __syncthreads();
     const int count = min(CHUNK, pos - base + 1);
 #pragma unroll
-    for (int part = 0; part < 2; part++) {
+    for (int part = 0; part < PARTS; part++) {
       const int e = tid + part * CHUNK;
       if (e < vdim) {
 #pragma unroll
@@ -168,10 +170,10 @@ multimap_attention_simple_kernel(const T* __restrict__ q, int q_stride, const T*
     }
     __syncthreads();
   }
-  float o[2];
+  float o[PARTS];
   float squares = 0.f;
 #pragma unroll
-  for (int part = 0; part < 2; part++) {
+  for (int part = 0; part < PARTS; part++) {
     o[part] = acc[0][part] / l_run[0];
     if (MAPS == 2) o[part] -= lambda * (acc[MAPS - 1][part] / l_run[MAPS - 1]);
     if (tid + part * CHUNK < vdim) squares = fmaf(o[part], o[part], squares);
@@ -180,7 +182,7 @@ multimap_attention_simple_kernel(const T* __restrict__ q, int q_stride, const T*
   if (norm_eps > 0.f) factor *= 1.0f / sqrtf(block_sum(squares, scratch) / (float)vdim + norm_eps);
   T* dst = out + (size_t)t * out_stride + (size_t)h * vdim;
 #pragma unroll
-  for (int part = 0; part < 2; part++)
+  for (int part = 0; part < PARTS; part++)
     if (tid + part * CHUNK < vdim) dst[tid + part * CHUNK] = from_float<T>(o[part] * factor);
 }
 
@@ -649,7 +651,7 @@ SPROUT_API int sprout_multimap_attention_simple(const void* q, int q_stride, con
   SPROUT_REQUIRE(tokens > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && page_tokens > 0 && num_pages > 0,
                  "multimap_attention: bad sizes");
   SPROUT_REQUIRE(maps == 1 || maps == 2, "multimap_attention: one or two maps per head (got %d)", maps);
-  SPROUT_REQUIRE(dim > 0 && vdim > 0 && vdim <= 2 * CHUNK, "multimap_attention: value rows of up to %d elements (got %d)", 2 * CHUNK, vdim);
+  SPROUT_REQUIRE(dim > 0 && vdim > 0 && vdim <= PARTS * CHUNK, "multimap_attention: value rows of up to %d elements (got %d)", PARTS * CHUNK, vdim);
   SPROUT_REQUIRE(heads <= 65535, "multimap_attention: too many heads");
   const size_t smem = (size_t)(maps * dim + maps * CHUNK + 36) * sizeof(float) + CHUNK * sizeof(long long);
   SPROUT_REQUIRE(smem <= 48 * 1024, "multimap_attention: key vectors too long (%d)", dim);

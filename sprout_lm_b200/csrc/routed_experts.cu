@@ -487,7 +487,7 @@ SPROUT_API int sprout_moe_route(const void* h, int h_stride, int dtype, const fl
   SPROUT_REQUIRE(h && router && correction && ids && weights && counts, "moe_route: null pointer");
   SPROUT_REQUIRE(tokens > 0 && width > 0 && outputs > 0 && experts >= 0 && experts <= outputs && top > 0 && top <= outputs,
                  "moe_route: bad sizes (outputs %d, experts %d, top %d)", outputs, experts, top);
-  const int per_block = tokens > 64 ? 8 : 1;
+  const int per_block = tokens > 64 && (size_t)8 * (2 * outputs + width) * sizeof(float) <= 200 * 1024 ? 8 : 1;
   const size_t smem = (size_t)per_block * (2 * outputs + width) * sizeof(float);
   SPROUT_REQUIRE(smem <= 200 * 1024, "moe_route: too many router outputs (%d) or too wide rows (%d)", outputs, width);
   static bool prepared = false;

@@ -35,8 +35,8 @@ class MultiMapAttention(Part):
             raise ValueError(f"multimap_attention: heads ({heads}) must be a positive multiple of kv_heads ({kv_heads})")
         if maps not in (1, 2):
             raise ValueError("multimap_attention: one or two maps per head")
-        if dim <= 0 or value_dim <= 0 or value_dim > 256:
-            raise ValueError("multimap_attention: dim must be positive and value_dim at most 256")
+        if dim <= 0 or value_dim <= 0 or value_dim > 512:
+            raise ValueError("multimap_attention: dim must be positive and value_dim at most 512")
         self.hidden_size, self.heads, self.kv_heads, self.dim, self.value_dim = hidden_size, heads, kv_heads, dim, value_dim
         self.maps, self.scale, self.diff = maps, float(scale), float(diff)
         self.norm_eps, self.out_scale, self.own_kv = float(norm_eps), float(out_scale), bool(own_kv)

@@ -113,7 +113,7 @@ def _fill_cache(kernels, dtype, contexts, G, maps, dim, vdim, page, cos, sin, rn
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("sizes", [(6, 2, 16, 24, 8, 16), (3, 3, 8, 8, 4, 8), (2, 1, 12, 40, 12, 16), (8, 4, 32, 64, 16, 16),
-                                   (8, 2, 64, 128, 32, 16), (3, 1, 16, 32, 8, 8), (2, 2, 128, 128, 64, 32)])
+                                   (8, 2, 64, 128, 32, 16), (3, 1, 16, 32, 8, 8), (2, 2, 128, 128, 64, 32), (2, 1, 8, 300, 4, 16)])
 def test_two_map_attention_over_pages(dtype, sizes):
     """Rotation, append and attention together: contexts on both sides of page and 128-key borders, a portion of
     queries and single queries, pages in shuffled order."""
